@@ -1,0 +1,453 @@
+#!/usr/bin/env python
+"""Benchmark of the gpt-oss attention hot path on B200: decode attention at gpt-oss-20b shapes.
+
+Workload (the configuration the metric is quoted on): 32 ragged sequences per GPU with KV
+lengths uniform in [1024, 8192] (seed 0), 64 query heads over 8 KV heads of width 64, a paged
+bf16 KV cache of 16-token pages handed out in scattered order, sinks N(0,1).  One step = one new
+token per sequence through one full-causal layer and one 128-token sliding-window layer:
+fused RoPE + append, then decode attention, for each layer.  Positions advance every step.
+
+Lines printed (rank 0): one JSON object with
+  value    - algorithmic HBM GB/s of the whole job, inputs resident in HBM, timed with CUDA
+             events on the launching stream (the batch's own event pair), max over ranks;
+  e2e      - the same metric through the host-buffer API: each step uploads that step's q, k, v,
+             positions and lengths from pinned host memory and reads the outputs back;
+  roofline - the dominant kernel (full-layer decode) alone, against the measured copy bandwidth;
+  cpu_baseline - the CPU oracle (a restatement of the reference's CPU path) on the host cores.
+
+With N > 1 (torchrun) the work is sharded by KV head and the batch grows with N (32 N sequences,
+8 / N KV heads of each on every GPU): per-GPU work is fixed, no collective is on the data path.
+
+`--impl reference` times the reference's CPU attention path (the oracle port: the reference is
+Rust and no Rust toolchain exists on these machines) on all host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEQS_PER_GPU = 32
+KV_HEADS, GROUP, D, PAGE = 8, 8, 64, 16
+WINDOW = 128
+LEN_LO, LEN_HI = 1024, 8192
+
+# DRAM bytes per launch of the full-layer decode kernel from the committed ncu capture
+# (profiles/), filled in after each capture; None until one exists for this workload.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(lens: np.ndarray, window: int, kv_heads: int = KV_HEADS) -> int:
+    """Per (sequence, layer, step): K and V of every visible key (2 * 64 * 2 bytes per key per KV
+    head), q in, out, and the new token's k, v read plus their cache write."""
+    n = np.minimum(lens, window) if window else lens
+    per_seq = 2 * D * 2 * kv_heads * n + kv_heads * (GROUP * D * 2 * 2 + 2 * D * 2 * 2)
+    return int(per_seq.sum())
+
+
+def draw_lengths(seqs: int) -> np.ndarray:
+    return np.random.default_rng(0).integers(LEN_LO, LEN_HI + 1, seqs).astype(np.int64)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.rows, self.proc = device, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, flag in zip(names, r[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, copy bandwidth)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's CPU path
+# ------------------------------------------------------------------------------------------
+def cpu_steps(lens: np.ndarray, threads: int, budget_s: float, min_steps: int = 1):
+    """Times whole steps of the workload (every sequence, both layers) on the CPU oracle until
+    `budget_s` is used.  Returns (seconds per step, steps timed)."""
+    from oracle import oracle
+    rng = np.random.default_rng(1)
+    seqs = len(lens)
+    sinks = rng.standard_normal(64).astype(np.float32)
+    rope = oracle.Rope()
+    sessions = []
+    for window in (0, WINDOW):
+        row = []
+        for length in lens:
+            s = oracle.Session(64, KV_HEADS, D, int(length) + max(64, min_steps) + 1, window=window, sinks=sinks, rope=rope,
+                               cache_bf16=True)
+            s.keys[:length] = oracle.round_bf16(rng.standard_normal((int(length), KV_HEADS, D)).astype(np.float32))
+            s.values[:length] = oracle.round_bf16(rng.standard_normal((int(length), KV_HEADS, D)).astype(np.float32))
+            s.len = int(length)
+            row.append(s)
+        sessions.append(row)
+    q = oracle.round_bf16(rng.standard_normal((seqs, 1, 64, D)).astype(np.float32))
+    k = oracle.round_bf16(rng.standard_normal((seqs, 1, KV_HEADS, D)).astype(np.float32))
+    v = oracle.round_bf16(rng.standard_normal((seqs, 1, KV_HEADS, D)).astype(np.float32))
+    times = []
+    began = time.perf_counter()
+    while len(times) < min_steps or (time.perf_counter() - began < budget_s and len(times) < 64):
+        t0 = time.perf_counter()
+        for row in sessions:
+            for i, s in enumerate(row):
+                s.feed(q[i], k[i], v[i], threads=threads)
+        times.append(time.perf_counter() - t0)
+    return float(np.mean(times)), len(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    cores = oracle.lib().oracle_max_threads()
+    lens = draw_lengths(SEQS_PER_GPU * args.gpus)
+    step_bytes = algorithmic_bytes(lens + 1, 0) + algorithmic_bytes(lens + 1, WINDOW)
+    # each "step" is one full step of the workload for the first sequences of the batch, as many
+    # as keep the whole run within a few minutes
+    sample = min(len(lens), 32)
+    sample_lens = lens[:sample]
+    sample_bytes = algorithmic_bytes(sample_lens + 1, 0) + algorithmic_bytes(sample_lens + 1, WINDOW)
+    for _ in range(args.warmup):
+        cpu_steps(sample_lens[:2], cores, 0.0)
+    per_step, _ = cpu_steps(sample_lens, cores, 0.0, min_steps=args.steps)
+    gbs = sample_bytes / per_step / 1e9
+    line = {
+        "impl": "reference", "metric": "decode attn HBM GB/s (gpt-oss-20b shapes)", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3 * (step_bytes / sample_bytes), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 storage, f32 accumulate", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} of {len(lens)} sequences, both layers, {args.steps} steps; "
+                                   "C restatement of gpt-oss/src/model.rs attention (no Rust toolchain here), "
+                                   "(position, head) pairs spread over all host threads"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tok_s": sample / per_step,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(gpus: int):
+    return {"workload": "decode attention, gpt-oss-20b shapes: one new token per sequence through one "
+                        "full-causal and one 128-window layer (fused RoPE+append, then attention)",
+            "global_batch": SEQS_PER_GPU * gpus, "kv_len": f"uniform[{LEN_LO},{LEN_HI}] seed 0",
+            "heads": "64q/8kv/hd64", "page_tokens": PAGE, "kv_cache": "paged bf16, scattered pages",
+            "parallelism": f"kv-head x{gpus} (batch grows with N)",
+            "l2": "inputs larger than L2: ~300 MB of KV read per step per GPU vs 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+class DecodeBench:
+    """Both layers of the workload on one GPU, with every step's small inputs laid out ahead of
+    time so that the resident run needs no host work between launches."""
+
+    def __init__(self, gpu, lens, kv_heads, total_steps):
+        from loadngo_b200 import compute
+        from loadngo_b200.layer import PagedAttentionLayer
+        from oracle import oracle  # only for bf16 rounding of the synthetic inputs
+        self.compute, self.gpu = compute, gpu
+        self.lens, self.kv_heads, self.heads = lens, kv_heads, kv_heads * GROUP
+        self.seqs = len(lens)
+        self.total_steps = total_steps
+        rng = np.random.default_rng(2)
+        max_ctx = int(lens.max()) + total_steps + 1
+        self.layers = []
+        for window in (0, WINDOW):
+            pool_pages = int(sum(-(-(int(l) + total_steps + 1) // PAGE) for l in lens)) + 4
+            layer = PagedAttentionLayer(gpu, seqs=self.seqs, max_context=max_ctx, max_new=self.seqs,
+                                        kv_heads=kv_heads, window=window,
+                                        sinks=rng.standard_normal(self.heads).astype(np.float32),
+                                        pool_pages=pool_pages, rng=rng)
+            for s, length in enumerate(lens):
+                layer.cache.reserve(s, int(length) + total_steps + 1)
+            layer.cache.lens[:] = lens
+            layer.cache.flush_table()
+            self._fill_pool(layer, rng)
+            self.layers.append(layer)
+        n, h, g = self.seqs, self.heads, kv_heads
+        bf = lambda shape: oracle.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32))
+        self.q_host, self.k_host, self.v_host = bf((n, h, D)), bf((n, g, D)), bf((n, g, D))
+        # per-step positions and lengths, all steps in one buffer
+        steps = np.arange(total_steps)[:, None]
+        self.pos_all = (lens[None, :] + steps).astype(np.int32)
+        self.len_all = self.pos_all + 1
+        for layer in self.layers:
+            layer.positions.free(); layer.seq_lens.free()
+            layer.positions = gpu.upload(self.pos_all)
+            layer.seq_lens = gpu.upload(self.len_all)
+            layer.q.write(self.q_host); layer.k.write(self.k_host); layer.v.write(self.v_host)
+            layer.seq_ids.write(np.arange(n, dtype=np.int32))
+
+    def _fill_pool(self, layer, rng):
+        """N(0,1) keys and values in every page (bf16), written chunk by chunk through a staging
+        buffer so the pool itself needs no host mirror."""
+        nbytes = len(layer.cache.pool)
+        chunk = 64 << 20
+        stage = self.gpu.buffer(min(chunk, nbytes))
+        done = 0
+        from oracle import oracle
+        while done < nbytes:
+            size = min(chunk, nbytes - done)
+            data = oracle.f32_to_bf16_bits(rng.standard_normal(size // 2).astype(np.float32))
+            stage.write(data)
+            # a one-dispatch batch copies the staged rows into place (copy_rows works on floats)
+            batch = self.gpu.batch([stage, layer.cache.pool])
+            batch.copy_rows((self.compute.Slice(0, 0, size), size // 4), (self.compute.Slice(1, done, size), size // 4),
+                            1, size // 4)
+            result = batch.run()
+            if isinstance(result.gpu_time, Exception):
+                raise result.gpu_time
+            done += size
+        stage.free()
+
+    def step_bytes(self, step: int) -> int:
+        lens = self.len_all[step].astype(np.int64)
+        return algorithmic_bytes(lens, 0, self.kv_heads) + algorithmic_bytes(lens, WINDOW, self.kv_heads)
+
+    def record_step(self, batch, layer_index, step, base):
+        """Records append + decode of one layer for step `step`; `base` is the position of that
+        layer's buffers in the batch."""
+        c = self.compute
+        layer = self.layers[layer_index]
+        n, h, g = self.seqs, self.heads, self.kv_heads
+        S = lambda i, off, ln: c.Slice(base + i, off, ln)
+        cache = c.PagedCache(S(layer.POOL, 0, len(layer.cache.pool)), S(layer.BT, 0, len(layer.cache.table)),
+                             layer.cache.max_pages, 0, g)
+        batch.rope_append_paged((S(layer.Q, 0, n * h * D * 2), S(layer.K, 0, n * g * D * 2), S(layer.V, 0, n * g * D * 2)),
+                                False, S(layer.QROT, 0, 2 * n * h * D * 2), S(layer.TABLE, 0, len(layer.table)), 0,
+                                S(layer.POS, step * n * 4, n * 4), S(layer.SEQ, 0, n * 4), cache, n)
+        batch.attention_decode_paged(S(layer.QROT, 0, 2 * n * h * D * 2), cache, S(layer.LENS, step * n * 4, n * 4), n,
+                                     int(self.len_all[step].max()), S(layer.SINKS, 0, h * 4), layer.window,
+                                     layer.scale, S(layer.OUT, 0, n * h * D * 2))
+
+    def all_buffers(self):
+        return self.layers[0].buffers() + self.layers[1].buffers()
+
+    def resident_run(self, first_step, steps, only_full_decode=False):
+        """`steps` steps in one batch, nothing crossing PCIe; returns GPU seconds (event pair on
+        the launching stream)."""
+        batch = self.gpu.batch(self.all_buffers())
+        nb = len(self.layers[0].buffers())
+        for i in range(steps):
+            if only_full_decode:
+                c, layer = self.compute, self.layers[0]
+                n, h, g = self.seqs, self.heads, self.kv_heads
+                S = lambda j, off, ln: c.Slice(j, off, ln)
+                cache = c.PagedCache(S(layer.POOL, 0, len(layer.cache.pool)), S(layer.BT, 0, len(layer.cache.table)),
+                                     layer.cache.max_pages, 0, g)
+                batch.attention_decode_paged(S(layer.QROT, 0, 2 * n * h * D * 2), cache,
+                                             S(layer.LENS, first_step * n * 4, n * 4), n,
+                                             int(self.len_all[first_step].max()), S(layer.SINKS, 0, h * 4), 0,
+                                             layer.scale, S(layer.OUT, 0, n * h * D * 2))
+            else:
+                self.record_step(batch, 0, first_step + i, 0)
+                self.record_step(batch, 1, first_step + i, nb)
+        launches = batch.dispatches
+        done = batch.run()
+        if isinstance(done.gpu_time, Exception):
+            raise done.gpu_time
+        return done.gpu_time, launches
+
+    def e2e_step(self, step):
+        """One step the way a caller with host data makes it: stage q, k, v, positions and
+        lengths in pinned memory, one batch for both layers, read both outputs back."""
+        n, h = self.seqs, self.heads
+        nb = len(self.layers[0].buffers())
+        for layer in self.layers:
+            layer.q.write(self.q_host); layer.k.write(self.k_host); layer.v.write(self.v_host)
+            layer.positions.write(self.pos_all[step], offset=step * n * 4)
+            layer.seq_lens.write(self.len_all[step], offset=step * n * 4)
+        batch = self.gpu.batch(self.all_buffers())
+        for li, base in ((0, 0), (1, nb)):
+            self.record_step(batch, li, step, base)
+            batch.read_back(self.compute.Slice(base + self.layers[li].OUT, 0, n * h * D * 2))
+        done = batch.run()
+        if isinstance(done.gpu_time, Exception):
+            raise done.gpu_time
+        outs = [layer.out.view(np.uint16)[: n * h * D] for layer in self.layers]
+        return int(outs[0][0]) + int(outs[1][0])  # touch the results on the host
+
+    def e2e_bytes(self):
+        n, h, g = self.seqs, self.heads, self.kv_heads
+        h2d = 2 * (n * h * D * 2 + 2 * n * g * D * 2 + 2 * n * 4)
+        d2h = 2 * n * h * D * 2
+        return h2d, d2h
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from loadngo_b200 import compute
+    from loadngo_b200.paged import shard_kv_heads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    gpu = compute.Gpu(local)
+    heads_here = shard_kv_heads(KV_HEADS, world, rank)
+    lens = draw_lengths(SEQS_PER_GPU * world)
+    total_steps = args.warmup + args.steps
+    bench = DecodeBench(gpu, lens, len(heads_here), total_steps * 3 + 2)
+
+    # ---- resident run: `value` ----------------------------------------------------------
+    bench.resident_run(0, args.warmup)
+    barrier()
+    with ClockSampler(local) as clocks:
+        gpu_s, launches = bench.resident_run(args.warmup, args.steps)
+        barrier()
+    gpu_s = max_over_ranks(gpu_s)
+    step_bytes_rank = float(np.mean([bench.step_bytes(args.warmup + i) for i in range(args.steps)]))
+    total_bytes = step_bytes_rank * world  # every rank reads its heads of every sequence: same bytes
+    value = total_bytes * args.steps / gpu_s / 1e9
+
+    # ---- dominant kernel alone: roofline -----------------------------------------------------
+    bench.resident_run(total_steps, 3, only_full_decode=True)
+    reps = max(args.steps, 20)
+    k_s, _ = bench.resident_run(total_steps, reps, only_full_decode=True)
+    full_bytes = algorithmic_bytes(bench.len_all[total_steps].astype(np.int64), 0, bench.kv_heads)
+    achieved = full_bytes / (k_s / reps) / 1e9
+    peak, peak_kind = measured_peak()
+
+    # ---- end to end through host buffers ---------------------------------------------------
+    base = total_steps + 1
+    for i in range(args.warmup):
+        bench.e2e_step(base + i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        bench.e2e_step(base + args.warmup + i)
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_value = total_bytes * args.steps / e2e_s / 1e9
+    h2d, d2h = bench.e2e_bytes()
+
+    if rank == 0:
+        clock = clocks.summary()
+        line = {
+            "metric": "decode attn HBM GB/s (gpt-oss-20b shapes)", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": gpu_s / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 storage, f32 accumulate", "data": "synthetic", "config": workload_config(world),
+            "tok_s_per_gpu": SEQS_PER_GPU * world * args.steps / gpu_s / world,
+            "gpu_launches": launches,
+            "clocks": clock,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s / args.steps * 1e3, "timed_with": "host clock around K steps, synchronised"},
+            "roofline": {"bound": "hbm", "kernel": "decode_kernel (full-causal layer)", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": full_bytes,
+                         "us_per_launch": k_s / reps * 1e6},
+        }
+        if world == 1 and not args.no_cpu:
+            from oracle import oracle
+            cores = 1
+            per_step, timed = cpu_steps(lens, cores, args.cpu_budget)
+            line["cpu_baseline"] = {
+                "value": step_bytes_rank / per_step / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"the whole step (32 sequences, both layers), {timed} steps, single thread as the "
+                          "reference's attention loop is (gpt-oss/src/model.rs:441-463); C restatement, "
+                          "no Rust toolchain on this machine",
+                "ms_per_step": per_step * 1e3}
+        print(json.dumps(line), flush=True)
+    barrier()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU baseline work")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,303 @@
+/*
+ * cuda_compute.h - C ABI of libcuda_compute.so: the gpt-oss attention hot path on NVIDIA B200
+ * (sm_100a), behind the kernel entry points loadngo's `gpt-oss` crate calls through its
+ * `metal-compute` crate.
+ *
+ * Everything here is `extern "C"`, plain pointers, sizes and scalars.  There is no CPU
+ * fallback: with no usable CUDA device every entry point that needs one returns
+ * CC_NO_DEVICE.  Each comment names the loadngo interface the entry replaces
+ * (path inside the loadngo repository : line).
+ *
+ * Two layers:
+ *   1. "Raw" entries take device pointers and a CUDA stream and only launch (section C).
+ *   2. Object entries mirror metal-compute's Gpu / Buffer / Resident / Batch / Slice
+ *      (sections D-F): a batch owns its buffers until the GPU is done, every dispatch is
+ *      validated before anything is launched, completion is delivered by callback.
+ *
+ * Return value of every `int` function: a cc_status.  After a non-zero status
+ * cc_last_error() holds a message for the calling thread.
+ */
+#ifndef CUDA_COMPUTE_H
+#define CUDA_COMPUTE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- A. Status -------------------------------------------------------------------------- */
+
+/* Mirrors `loadngo_metal_compute::Error` (metal-compute/src/lib.rs:42-53). */
+typedef enum cc_status {
+    CC_OK = 0,
+    CC_NO_DEVICE = 1, /* Error::NoDevice */
+    CC_COMPILE = 2,   /* Error::Compile: the library's kernels could not be loaded on this device */
+    CC_ALLOC = 3,     /* Error::Alloc(len) */
+    CC_DISPATCH = 4,  /* Error::Dispatch(text): rejected before anything was launched */
+    CC_GPU = 5        /* Error::Gpu(text): the submitted work failed */
+} cc_status;
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char *cc_last_error(void);
+/* Library version, e.g. "0.1.0". */
+const char *cc_version(void);
+
+/* ---- B. YaRN rotary table (host arithmetic, no device needed) ----------------------------- */
+
+/* gpt-oss's rotary parameters: `Config` fields rope_theta, rope_factor,
+ * rope_original_context, head_dim (gpt-oss/src/config.rs:5-25) and the two YaRN ramp
+ * constants (config.rs:30-31). */
+typedef struct cc_rope_params {
+    uint32_t head_dim;
+    double theta;
+    double factor;
+    double original_context;
+    double beta_fast;
+    double beta_slow;
+} cc_rope_params;
+
+/* `Config::rope` (gpt-oss/src/config.rs:108-133): head_dim/2 inverse frequencies and the
+ * factor applied to every cosine and sine. */
+int cc_yarn_inv_freq(const cc_rope_params *params, double *inv_freq, double *scale);
+
+/* The (cos, sin) table `GpuModel::prepare` fills (gpt-oss/src/gpu.rs:689-697): `rows` rows
+ * of head_dim/2 float pairs for positions start, start+1, ...; angle and factor in double,
+ * one cast to float. */
+int cc_rope_table(const cc_rope_params *params, uint64_t start, uint64_t rows, float *table);
+
+/* ---- C. Raw entries: device pointers + stream --------------------------------------------- */
+
+/* Paged bf16 KV cache ("pool"): pool[page][kv_head][2][16][64] bfloat16.  Per (page, kv head)
+ * a 4 KiB tile: 16 key rows then 16 value rows of 64.  A sequence's position p lives in page
+ * block_table[seq][p / 16] (or [(p / 16) % ring_pages] when ring_pages != 0, the paged form of
+ * metal-compute's ring of `slots` rows, apple.rs:608-612), row p % 16.  The pool pointer must
+ * be 128-byte aligned. */
+#define CC_PAGE_TOKENS 16u
+#define CC_HEAD_DIM 64u
+#define CC_GROUP 8u
+
+/* Fused RoPE + KV append.  Replaces Batch::rotate_halves on Q and K
+ * (metal-compute/src/apple.rs:1916-1955, kernel kernels.metal:1672-1690) and the
+ * Batch::copy_rows pair that appends K and V (gpt-oss/src/gpu.rs:744-759); arithmetic of
+ * Model::rotate (gpt-oss/src/model.rs:389-404).  All pointers are device pointers. */
+typedef struct cc_rope_append_args {
+    const void *q;             /* [n][heads][64] */
+    const void *k;             /* [n][kv_heads][64] */
+    const void *v;             /* [n][kv_heads][64] */
+    uint32_t in_f32;           /* 0: q,k,v are bfloat16; 1: float */
+    void *q_hi;                /* out [n][heads][64] bf16: rotated q rounded to bf16 */
+    void *q_lo;                /* out [n][heads][64] bf16: rotated q minus q_hi; may be NULL */
+    const float *table;        /* [table_rows][32][2] from cc_rope_table */
+    uint64_t table_start;      /* position of table row 0 */
+    uint64_t table_rows;
+    const int32_t *positions;  /* [n] absolute position of each new token */
+    const int32_t *seq_ids;    /* [n] block_table row of each new token */
+    void *pool;
+    uint32_t pool_pages;
+    const int32_t *block_table; /* [seqs][max_pages] */
+    uint32_t max_pages;
+    uint32_t ring_pages;
+    uint32_t n;
+    uint32_t heads;            /* = 8 * kv_heads */
+    uint32_t kv_heads;
+    uint32_t *status;          /* device word the kernel raises on bad pages/rows; may be NULL */
+} cc_rope_append_args;
+int cc_rope_append_paged(void *stream, const cc_rope_append_args *args);
+
+/* Decode attention: one query position per sequence.  Replaces
+ * Batch::attention_grouped_with_sinks for t = 1 (metal-compute/src/apple.rs:1213-1289, kernel
+ * `attention_grouped_narrow` kernels.metal:1944-2032); arithmetic of the CPU reference
+ * (gpt-oss/src/model.rs:441-463). */
+typedef struct cc_decode_args {
+    const void *q_hi;           /* [seqs][heads][64] bf16 (from cc_rope_append_paged) */
+    const void *q_lo;           /* same shape, or NULL */
+    const void *pool;
+    uint32_t pool_pages;
+    const int32_t *block_table; /* [seqs][max_pages] */
+    uint32_t max_pages;
+    uint32_t ring_pages;
+    const int32_t *seq_lens;    /* [seqs] keys stored for the sequence, the new one included;
+                                   the query is the last of them */
+    uint32_t seqs;
+    uint32_t max_seq_len;       /* host-side upper bound of seq_lens (sizes the grid) */
+    const float *sinks;         /* [heads] or NULL */
+    uint32_t heads;
+    uint32_t kv_heads;
+    uint32_t window;            /* keys each query sees, itself included; 0 = all */
+    float scale;
+    void *out;                  /* [seqs][heads][64] bf16 */
+    void *workspace;            /* scratch, see cc_decode_workspace_bytes; zero it once before
+                                   first use, the kernel leaves it reusable */
+    size_t workspace_bytes;
+    uint32_t pages_per_split;   /* 0 = choose */
+    uint32_t *status;           /* may be NULL */
+} cc_decode_args;
+int cc_attention_decode_paged(void *stream, const cc_decode_args *args);
+/* Scratch bytes cc_attention_decode_paged needs for these sizes. */
+size_t cc_decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_seq_len, uint32_t window,
+                                 uint32_t pages_per_split);
+
+/* Prefill attention: t_b new positions per sequence against the cache (which already holds
+ * them: call cc_rope_append_paged first).  Replaces Batch::attention_grouped_tiled_with_sinks
+ * (metal-compute/src/apple.rs:1324-1401, kernel `attention_grouped_tiled`
+ * kernels.metal:588-720). */
+typedef struct cc_prefill_args {
+    const void *q_hi;           /* [total_tokens][heads][64] bf16, sequences back to back */
+    const void *q_lo;           /* same shape or NULL (adds the low-order query bits) */
+    const void *pool;
+    uint32_t pool_pages;
+    const int32_t *block_table; /* [seqs][max_pages] */
+    uint32_t max_pages;
+    uint32_t ring_pages;
+    const int32_t *q_offsets;   /* [seqs + 1] first token row of each sequence in q/out */
+    const int32_t *starts;      /* [seqs] absolute position of each sequence's first new token */
+    uint32_t seqs;
+    uint32_t max_t;             /* host-side upper bound of the new positions per sequence */
+    const float *sinks;
+    uint32_t heads;
+    uint32_t kv_heads;
+    uint32_t window;
+    float scale;
+    void *out;                  /* [total_tokens][heads][64] bf16 */
+    uint32_t *status;
+} cc_prefill_args;
+int cc_attention_prefill_paged(void *stream, const cc_prefill_args *args);
+
+/* ---- D. Gpu, Buffer, Resident -------------------------------------------------------------- */
+
+typedef struct cc_gpu cc_gpu;           /* metal-compute/src/apple.rs:72 `Gpu` */
+typedef struct cc_buffer cc_buffer;     /* apple.rs:391 `Buffer` */
+typedef struct cc_resident cc_resident; /* apple.rs:432 `Resident` */
+typedef struct cc_batch cc_batch;       /* apple.rs:523 `Batch` */
+
+/* Gpu::new (apple.rs:105): opens CUDA device `device`, its stream and completion thread. */
+int cc_gpu_new(int device, cc_gpu **out);
+void cc_gpu_free(cc_gpu *gpu);
+/* The stream every batch of this gpu runs on (a cudaStream_t). */
+void *cc_gpu_stream(cc_gpu *gpu);
+/* Blocks until everything committed so far has finished and its callbacks have run. */
+int cc_gpu_synchronize(cc_gpu *gpu);
+
+/* Gpu::buffer (apple.rs:255-272): `len` bytes the CPU and GPU share: device memory plus a
+ * pinned host mirror.  Contents unspecified until written. */
+int cc_buffer_new(cc_gpu *gpu, size_t len, cc_buffer **out);
+/* Device memory only (KV pools too large to mirror); as_bytes on it fails. */
+int cc_buffer_new_device(cc_gpu *gpu, size_t len, cc_buffer **out);
+void cc_buffer_free(cc_buffer *buffer);
+size_t cc_buffer_len(const cc_buffer *buffer);
+/* Buffer::as_bytes (apple.rs:410-414): the host view, brought up to date with what the GPU
+ * last wrote.  NULL while a batch owns the buffer. */
+const void *cc_buffer_as_bytes(cc_buffer *buffer);
+/* Buffer::as_bytes_mut (apple.rs:416-419): as above, and the next batch uploads the buffer. */
+void *cc_buffer_as_bytes_mut(cc_buffer *buffer);
+/* Like as_bytes_mut for one byte range: only that range is uploaded. */
+void *cc_buffer_write_range(cc_buffer *buffer, size_t offset, size_t len);
+/* The device address (for raw entries). */
+void *cc_buffer_device_ptr(cc_buffer *buffer);
+/* Fills the whole buffer with zero bytes on the device (and the mirror). */
+int cc_buffer_zero(cc_buffer *buffer);
+
+/* Gpu::resident (apple.rs:297-300): read-only device memory filled once from `bytes`,
+ * 256-byte aligned. */
+int cc_resident_new(cc_gpu *gpu, const void *bytes, size_t len, cc_resident **out);
+void cc_resident_free(cc_resident *resident);
+size_t cc_resident_len(const cc_resident *resident);
+
+/* ---- E. Batch -------------------------------------------------------------------------------- */
+
+/* `Slice` (apple.rs:507-521): bytes of buffer `buffer` of the batch (positions in the vector
+ * given to cc_batch_begin; attached residents follow). */
+typedef struct cc_slice {
+    uint32_t buffer;
+    uint64_t offset;
+    uint64_t len;
+} cc_slice;
+
+/* `GroupedShape` (apple.rs:596-614).  window = UINT64_MAX: every earlier position. */
+typedef struct cc_grouped_shape {
+    uint64_t t;
+    uint64_t start;
+    uint64_t heads;
+    uint64_t kv_heads;
+    uint64_t dim;
+    uint64_t window;
+    uint64_t slots;
+    float scale;
+} cc_grouped_shape;
+
+#define CC_DISPATCH_SERIAL 0     /* `Dispatch::Serial` (apple.rs:66-69) */
+#define CC_DISPATCH_CONCURRENT 1 /* `Dispatch::Concurrent`: ordered here too (stream order) */
+
+/* Gpu::batch (apple.rs:365-385): starts recording; the batch owns `buffers` until it
+ * completes or is dropped. */
+int cc_batch_begin(cc_gpu *gpu, cc_buffer *const *buffers, uint32_t count, int dispatch, cc_batch **out);
+/* Batch::attach (apple.rs:835-848). */
+int cc_batch_attach(cc_batch *batch, cc_resident *resident, cc_slice *out);
+/* Batch::copy_rows (apple.rs:1762-1788): `width` floats of each of `rows` rows. */
+int cc_batch_copy_rows(cc_batch *batch, cc_slice src, uint64_t src_stride, cc_slice dst, uint64_t dst_stride,
+                       uint64_t rows, uint64_t width);
+/* Batch::rmsnorm_rows (apple.rs:1733-1758): v = w * v / sqrt(mean(v^2) + eps) in place. */
+int cc_batch_rmsnorm_rows(cc_batch *batch, cc_slice v, cc_slice w, uint64_t rows, uint64_t d, uint64_t stride,
+                          float eps);
+/* Batch::add_rows (apple.rs:1886-1911): dst[r] += src[r * src_stride ..]; stride 0 = a bias. */
+int cc_batch_add_rows(cc_batch *batch, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
+                      uint64_t width);
+/* Batch::rotate_halves (apple.rs:1916-1924): rotary by halves in place from a (cos, sin) table. */
+int cc_batch_rotate_halves(cc_batch *batch, cc_slice x, cc_slice table, uint64_t rows, uint64_t heads,
+                           uint64_t dim);
+/* Batch::attention_grouped / _with_sinks (apple.rs:1199-1289): float q, k, v, out; keys and
+ * values in a ring of `slots` rows.  `sinks` may be NULL. */
+int cc_batch_attention_grouped(cc_batch *batch, cc_slice q, cc_slice k, cc_slice v, const cc_slice *sinks,
+                               cc_slice out, const cc_grouped_shape *shape);
+/* Batch::attention_grouped_tiled / _with_sinks (apple.rs:1311-1401): the prompt-pass form;
+ * q and out hold t rounded up to 32 rows, k and v rows up to the next multiple of 32. */
+int cc_batch_attention_grouped_tiled(cc_batch *batch, cc_slice q, cc_slice k, cc_slice v, const cc_slice *sinks,
+                                     cc_slice out, const cc_grouped_shape *shape);
+/* Batch::barrier (apple.rs:2194-2198). */
+int cc_batch_barrier(cc_batch *batch);
+
+/* The paged bf16 path on slices: same arguments as the raw entries, each pointer replaced by a
+ * slice of the batch.  `positions`, `seq_ids`, `block_table`, `seq_lens`, `q_offsets`, `starts`
+ * are int32 arrays inside buffers. */
+typedef struct cc_paged_cache {
+    cc_slice pool;
+    cc_slice block_table; /* [seqs][max_pages] int32 */
+    uint32_t max_pages;
+    uint32_t ring_pages;
+    uint32_t kv_heads;
+} cc_paged_cache;
+int cc_batch_rope_append_paged(cc_batch *batch, cc_slice q, cc_slice k, cc_slice v, uint32_t in_f32, cc_slice q_rot,
+                               cc_slice table, uint64_t table_start, cc_slice positions, cc_slice seq_ids,
+                               const cc_paged_cache *cache, uint32_t n);
+int cc_batch_attention_decode_paged(cc_batch *batch, cc_slice q_rot, const cc_paged_cache *cache,
+                                    cc_slice seq_lens, uint32_t seqs, uint32_t max_seq_len, const cc_slice *sinks,
+                                    uint32_t window, float scale, cc_slice out);
+int cc_batch_attention_prefill_paged(cc_batch *batch, cc_slice q_rot, const cc_paged_cache *cache,
+                                     cc_slice q_offsets, cc_slice starts, uint32_t seqs, uint32_t total_tokens,
+                                     uint32_t max_t, const cc_slice *sinks, uint32_t window, float scale,
+                                     cc_slice out);
+
+/* Asks for `slice` to be copied to its buffer's host mirror as part of the batch, so that
+ * cc_buffer_as_bytes after completion does not wait. */
+int cc_batch_read_back(cc_batch *batch, cc_slice slice);
+
+/* `Completed` (apple.rs:536-539): status CC_OK or CC_GPU, message, GPU seconds between the
+ * batch's first and last command. Runs on the gpu's completion thread. */
+typedef void (*cc_completion_fn)(void *user, int status, const char *message, double gpu_seconds);
+/* Batch::commit (apple.rs:2202-2239): submits and returns at once; the buffers are handed
+ * back (usable on the host again) just before `done` runs.  Frees the batch. */
+int cc_batch_commit(cc_batch *batch, cc_completion_fn done, void *user);
+/* Commit and wait on the calling thread. */
+int cc_batch_commit_wait(cc_batch *batch, double *gpu_seconds);
+/* Dropping a batch (apple.rs:553-561): nothing recorded runs... see INTEGRATION notes: work
+ * already enqueued is waited for, buffers are handed back, no callback. */
+void cc_batch_drop(cc_batch *batch);
+/* Dispatches recorded so far. */
+uint32_t cc_batch_dispatches(const cc_batch *batch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUDA_COMPUTE_H */

@@ -1,0 +1,453 @@
+"""ctypes mirror of `loadngo_metal_compute`'s public types over libcuda_compute.so.
+
+Same names and argument meaning as the Rust crate the `gpt-oss` crate calls
+(metal-compute/src/apple.rs): `Gpu`, `Buffer`, `Resident`, `Slice`, `Batch`, `Dispatch`,
+`GroupedShape`, and `Error` with the variants of metal-compute/src/lib.rs:42-53.  It exists so
+that tests and the benchmark can drive the C ABI the way the Rust caller would; it holds no
+arithmetic of its own and there is no fallback: if the shared library is missing, importing
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_float, c_int, c_int32,
+                    c_size_t, c_uint32, c_uint64, c_void_p)
+from dataclasses import dataclass
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcuda_compute.so")
+
+FULL = 2 ** 64 - 1  # `usize::MAX`: a window over every earlier position
+
+
+class Error(Exception):
+    """`loadngo_metal_compute::Error` (metal-compute/src/lib.rs:42-53)."""
+    code = 0
+
+
+class NoDevice(Error):
+    code = 1
+
+
+class Compile(Error):
+    code = 2
+
+
+class Alloc(Error):
+    code = 3
+
+
+class DispatchError(Error):
+    code = 4
+
+
+class GpuError(Error):
+    code = 5
+
+
+_ERRORS = {c.code: c for c in (NoDevice, Compile, Alloc, DispatchError, GpuError)}
+
+
+class Slice(Structure):
+    """`Slice` (apple.rs:507-521): bytes `offset .. offset + len` of buffer `buffer`."""
+    _fields_ = [("buffer", c_uint32), ("offset", c_uint64), ("len", c_uint64)]
+
+    def __init__(self, buffer: int = 0, offset: int = 0, len: int = 0):  # noqa: A002
+        super().__init__(buffer, offset, len)
+
+
+class _GroupedShape(Structure):
+    _fields_ = [("t", c_uint64), ("start", c_uint64), ("heads", c_uint64), ("kv_heads", c_uint64),
+                ("dim", c_uint64), ("window", c_uint64), ("slots", c_uint64), ("scale", c_float)]
+
+
+@dataclass
+class GroupedShape:
+    """`GroupedShape` (apple.rs:596-614)."""
+    t: int
+    start: int
+    heads: int
+    kv_heads: int
+    dim: int
+    window: int
+    slots: int
+    scale: float
+
+    def _c(self) -> _GroupedShape:
+        return _GroupedShape(self.t, self.start, self.heads, self.kv_heads, self.dim,
+                             min(self.window, FULL), self.slots, self.scale)
+
+
+class RopeParams(Structure):
+    _fields_ = [("head_dim", c_uint32), ("theta", c_double), ("factor", c_double),
+                ("original_context", c_double), ("beta_fast", c_double), ("beta_slow", c_double)]
+
+
+class RopeAppendArgs(Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("in_f32", c_uint32),
+                ("q_hi", c_void_p), ("q_lo", c_void_p), ("table", c_void_p),
+                ("table_start", c_uint64), ("table_rows", c_uint64), ("positions", c_void_p),
+                ("seq_ids", c_void_p), ("pool", c_void_p), ("pool_pages", c_uint32),
+                ("block_table", c_void_p), ("max_pages", c_uint32), ("ring_pages", c_uint32),
+                ("n", c_uint32), ("heads", c_uint32), ("kv_heads", c_uint32), ("status", c_void_p)]
+
+
+class DecodeArgs(Structure):
+    _fields_ = [("q_hi", c_void_p), ("q_lo", c_void_p), ("pool", c_void_p), ("pool_pages", c_uint32),
+                ("block_table", c_void_p), ("max_pages", c_uint32), ("ring_pages", c_uint32),
+                ("seq_lens", c_void_p), ("seqs", c_uint32), ("max_seq_len", c_uint32),
+                ("sinks", c_void_p), ("heads", c_uint32), ("kv_heads", c_uint32),
+                ("window", c_uint32), ("scale", c_float), ("out", c_void_p),
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+                ("pages_per_split", c_uint32), ("status", c_void_p)]
+
+
+class PrefillArgs(Structure):
+    _fields_ = [("q_hi", c_void_p), ("q_lo", c_void_p), ("pool", c_void_p), ("pool_pages", c_uint32),
+                ("block_table", c_void_p), ("max_pages", c_uint32), ("ring_pages", c_uint32),
+                ("q_offsets", c_void_p), ("starts", c_void_p), ("seqs", c_uint32),
+                ("max_t", c_uint32), ("sinks", c_void_p), ("heads", c_uint32),
+                ("kv_heads", c_uint32), ("window", c_uint32), ("scale", c_float),
+                ("out", c_void_p), ("status", c_void_p)]
+
+
+class PagedCache(Structure):
+    _fields_ = [("pool", Slice), ("block_table", Slice), ("max_pages", c_uint32),
+                ("ring_pages", c_uint32), ("kv_heads", c_uint32)]
+
+
+COMPLETION_FN = ctypes.CFUNCTYPE(None, c_void_p, c_int, c_char_p, c_double)
+
+# name -> (restype, argtypes): every symbol include/cuda_compute.h declares.
+SYMBOLS = {
+    "cc_last_error": (c_char_p, []),
+    "cc_version": (c_char_p, []),
+    "cc_yarn_inv_freq": (c_int, [POINTER(RopeParams), POINTER(c_double), POINTER(c_double)]),
+    "cc_rope_table": (c_int, [POINTER(RopeParams), c_uint64, c_uint64, c_void_p]),
+    "cc_rope_append_paged": (c_int, [c_void_p, POINTER(RopeAppendArgs)]),
+    "cc_attention_decode_paged": (c_int, [c_void_p, POINTER(DecodeArgs)]),
+    "cc_decode_workspace_bytes": (c_size_t, [c_uint32, c_uint32, c_uint32, c_uint32, c_uint32]),
+    "cc_attention_prefill_paged": (c_int, [c_void_p, POINTER(PrefillArgs)]),
+    "cc_gpu_new": (c_int, [c_int, POINTER(c_void_p)]),
+    "cc_gpu_free": (None, [c_void_p]),
+    "cc_gpu_stream": (c_void_p, [c_void_p]),
+    "cc_gpu_synchronize": (c_int, [c_void_p]),
+    "cc_buffer_new": (c_int, [c_void_p, c_size_t, POINTER(c_void_p)]),
+    "cc_buffer_new_device": (c_int, [c_void_p, c_size_t, POINTER(c_void_p)]),
+    "cc_buffer_free": (None, [c_void_p]),
+    "cc_buffer_len": (c_size_t, [c_void_p]),
+    "cc_buffer_as_bytes": (c_void_p, [c_void_p]),
+    "cc_buffer_as_bytes_mut": (c_void_p, [c_void_p]),
+    "cc_buffer_write_range": (c_void_p, [c_void_p, c_size_t, c_size_t]),
+    "cc_buffer_device_ptr": (c_void_p, [c_void_p]),
+    "cc_buffer_zero": (c_int, [c_void_p]),
+    "cc_resident_new": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_void_p)]),
+    "cc_resident_free": (None, [c_void_p]),
+    "cc_resident_len": (c_size_t, [c_void_p]),
+    "cc_batch_begin": (c_int, [c_void_p, POINTER(c_void_p), c_uint32, c_int, POINTER(c_void_p)]),
+    "cc_batch_attach": (c_int, [c_void_p, c_void_p, POINTER(Slice)]),
+    "cc_batch_copy_rows": (c_int, [c_void_p, Slice, c_uint64, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_rmsnorm_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64, c_float]),
+    "cc_batch_add_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_rotate_halves": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_attention_grouped": (c_int, [c_void_p, Slice, Slice, Slice, POINTER(Slice), Slice,
+                                           POINTER(_GroupedShape)]),
+    "cc_batch_attention_grouped_tiled": (c_int, [c_void_p, Slice, Slice, Slice, POINTER(Slice), Slice,
+                                                 POINTER(_GroupedShape)]),
+    "cc_batch_barrier": (c_int, [c_void_p]),
+    "cc_batch_rope_append_paged": (c_int, [c_void_p, Slice, Slice, Slice, c_uint32, Slice, Slice,
+                                           c_uint64, Slice, Slice, POINTER(PagedCache), c_uint32]),
+    "cc_batch_attention_decode_paged": (c_int, [c_void_p, Slice, POINTER(PagedCache), Slice, c_uint32,
+                                                c_uint32, POINTER(Slice), c_uint32, c_float, Slice]),
+    "cc_batch_attention_prefill_paged": (c_int, [c_void_p, Slice, POINTER(PagedCache), Slice, Slice,
+                                                 c_uint32, c_uint32, c_uint32, POINTER(Slice),
+                                                 c_uint32, c_float, Slice]),
+    "cc_batch_read_back": (c_int, [c_void_p, Slice]),
+    "cc_batch_commit": (c_int, [c_void_p, COMPLETION_FN, c_void_p]),
+    "cc_batch_commit_wait": (c_int, [c_void_p, POINTER(c_double)]),
+    "cc_batch_drop": (None, [c_void_p]),
+    "cc_batch_dispatches": (c_uint32, [c_void_p]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libcuda_compute.so and types every symbol; raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is not built (run __graft_entry__.build())")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise _ERRORS.get(code, Error)(lib().cc_last_error().decode())
+
+
+def rope_table(start: int, rows: int, *, head_dim=64, theta=150000.0, factor=32.0,
+               original_context=4096.0, beta_fast=32.0, beta_slow=1.0) -> np.ndarray:
+    """The (cos, sin) table of gpt-oss/src/gpu.rs:689-697, computed by the library's host code."""
+    params = RopeParams(head_dim, theta, factor, original_context, beta_fast, beta_slow)
+    out = np.zeros((rows, head_dim // 2, 2), np.float32)
+    check(lib().cc_rope_table(byref(params), start, rows, out.ctypes.data))
+    return out
+
+
+def yarn_inv_freq(*, head_dim=64, theta=150000.0, factor=32.0, original_context=4096.0,
+                  beta_fast=32.0, beta_slow=1.0):
+    params = RopeParams(head_dim, theta, factor, original_context, beta_fast, beta_slow)
+    inv = (c_double * (head_dim // 2))()
+    scale = c_double()
+    check(lib().cc_yarn_inv_freq(byref(params), inv, byref(scale)))
+    return np.array(inv[:], np.float64), scale.value
+
+
+class Buffer:
+    """`Buffer` (apple.rs:388-430): memory the CPU and the GPU share."""
+
+    def __init__(self, gpu: "Gpu", handle: int, mirrored: bool):
+        self._gpu, self._h, self._mirrored = gpu, handle, mirrored
+
+    def __len__(self) -> int:
+        return lib().cc_buffer_len(self._h)
+
+    def _view(self, ptr, dtype):
+        if not ptr:
+            raise DispatchError(lib().cc_last_error().decode())
+        n = len(self)
+        raw = (ctypes.c_uint8 * n).from_address(ptr)
+        arr = np.frombuffer(raw, np.uint8)
+        return arr[: n - n % np.dtype(dtype).itemsize].view(dtype)
+
+    def as_bytes(self) -> np.ndarray:
+        return self._view(lib().cc_buffer_as_bytes(self._h), np.uint8)
+
+    def as_bytes_mut(self) -> np.ndarray:
+        return self._view(lib().cc_buffer_as_bytes_mut(self._h), np.uint8)
+
+    def as_f32(self) -> np.ndarray:
+        return self._view(lib().cc_buffer_as_bytes(self._h), np.float32)
+
+    def as_f32_mut(self) -> np.ndarray:
+        return self._view(lib().cc_buffer_as_bytes_mut(self._h), np.float32)
+
+    def view(self, dtype, mutable: bool = False) -> np.ndarray:
+        fn = lib().cc_buffer_as_bytes_mut if mutable else lib().cc_buffer_as_bytes
+        return self._view(fn(self._h), dtype)
+
+    def write(self, array: np.ndarray, offset: int = 0) -> None:
+        """Copies `array`'s bytes to `offset` and marks just that range for upload."""
+        data = np.ascontiguousarray(array).view(np.uint8).reshape(-1)
+        ptr = lib().cc_buffer_write_range(self._h, offset, data.size)
+        if not ptr:
+            raise DispatchError(lib().cc_last_error().decode())
+        ctypes.memmove(ptr, data.ctypes.data, data.size)
+
+    def zero(self) -> None:
+        check(lib().cc_buffer_zero(self._h))
+
+    @property
+    def device_ptr(self) -> int:
+        return lib().cc_buffer_device_ptr(self._h)
+
+    def free(self) -> None:
+        if self._h:
+            lib().cc_buffer_free(self._h)
+            self._h = None
+
+
+class Resident:
+    """`Resident` (apple.rs:432-435): read-only device memory filled once."""
+
+    def __init__(self, handle: int):
+        self._h = handle
+
+    def __len__(self) -> int:
+        return lib().cc_resident_len(self._h)
+
+    def free(self) -> None:
+        if self._h:
+            lib().cc_resident_free(self._h)
+            self._h = None
+
+
+class Dispatch:
+    """`Dispatch` (apple.rs:61-70)."""
+    Serial = 0
+    Concurrent = 1
+
+
+@dataclass
+class Completed:
+    """`Completed` (apple.rs:536-539): the buffers come back with the GPU time or the error."""
+    buffers: list
+    gpu_time: float | Error
+
+
+class Gpu:
+    """`Gpu` (apple.rs:72-385) over one CUDA device."""
+
+    def __init__(self, device: int = 0):
+        h = c_void_p()
+        check(lib().cc_gpu_new(device, byref(h)))
+        self._h = h.value
+        self.device = device
+
+    @property
+    def stream(self) -> int:
+        return lib().cc_gpu_stream(self._h)
+
+    def synchronize(self) -> None:
+        check(lib().cc_gpu_synchronize(self._h))
+
+    def buffer(self, length: int) -> Buffer:
+        h = c_void_p()
+        check(lib().cc_buffer_new(self._h, length, byref(h)))
+        return Buffer(self, h.value, True)
+
+    def device_buffer(self, length: int) -> Buffer:
+        h = c_void_p()
+        check(lib().cc_buffer_new_device(self._h, length, byref(h)))
+        return Buffer(self, h.value, False)
+
+    def upload(self, array: np.ndarray) -> Buffer:
+        data = np.ascontiguousarray(array)
+        b = self.buffer(max(data.nbytes, 1))
+        b.write(data)
+        return b
+
+    def resident(self, data) -> Resident:
+        raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        h = c_void_p()
+        check(lib().cc_resident_new(self._h, raw.ctypes.data, raw.size, byref(h)))
+        return Resident(h.value)
+
+    def batch(self, buffers: list, dispatch: int = Dispatch.Serial) -> "Batch":
+        arr = (c_void_p * max(len(buffers), 1))(*[b._h for b in buffers])
+        h = c_void_p()
+        check(lib().cc_batch_begin(self._h, arr, len(buffers), dispatch, byref(h)))
+        return Batch(self, h.value, list(buffers))
+
+    def free(self) -> None:
+        if self._h:
+            lib().cc_gpu_free(self._h)
+            self._h = None
+
+
+def _opt(slice_or_none):
+    return None if slice_or_none is None else byref(slice_or_none)
+
+
+class Batch:
+    """`Batch` (apple.rs:523-2239): records dispatches, each validated before anything is
+    launched; `commit` submits them all."""
+
+    def __init__(self, gpu: Gpu, handle: int, buffers: list):
+        self._gpu, self._h, self._buffers = gpu, handle, buffers
+        self._keep = []
+
+    def attach(self, resident: Resident) -> Slice:
+        out = Slice()
+        check(lib().cc_batch_attach(self._h, resident._h, byref(out)))
+        return out
+
+    def copy_rows(self, src, dst, rows: int, width: int) -> None:
+        (s, ss), (d, ds) = src, dst
+        check(lib().cc_batch_copy_rows(self._h, s, ss, d, ds, rows, width))
+
+    def rmsnorm_rows(self, vw, rows: int, d_stride, eps: float) -> None:
+        (v, w), (d, stride) = vw, d_stride
+        check(lib().cc_batch_rmsnorm_rows(self._h, v, w, rows, d, stride, eps))
+
+    def add_rows(self, dst: Slice, src, rows: int, width: int) -> None:
+        s, ss = src
+        check(lib().cc_batch_add_rows(self._h, dst, s, ss, rows, width))
+
+    def rotate_halves(self, x: Slice, table: Slice, rows: int, heads_dim) -> None:
+        heads, dim = heads_dim
+        check(lib().cc_batch_rotate_halves(self._h, x, table, rows, heads, dim))
+
+    def attention_grouped(self, q, k, v, out, shape: GroupedShape) -> None:
+        check(lib().cc_batch_attention_grouped(self._h, q, k, v, None, out, byref(shape._c())))
+
+    def attention_grouped_with_sinks(self, qkv, sinks: Slice, out: Slice, shape: GroupedShape) -> None:
+        q, k, v = qkv
+        check(lib().cc_batch_attention_grouped(self._h, q, k, v, byref(sinks), out, byref(shape._c())))
+
+    def attention_grouped_tiled(self, q, k, v, out, shape: GroupedShape) -> None:
+        check(lib().cc_batch_attention_grouped_tiled(self._h, q, k, v, None, out, byref(shape._c())))
+
+    def attention_grouped_tiled_with_sinks(self, qkv, sinks: Slice, out: Slice, shape: GroupedShape) -> None:
+        q, k, v = qkv
+        check(lib().cc_batch_attention_grouped_tiled(self._h, q, k, v, byref(sinks), out,
+                                                     byref(shape._c())))
+
+    def barrier(self) -> None:
+        check(lib().cc_batch_barrier(self._h))
+
+    # -- the paged bf16 path --------------------------------------------------------------
+    def rope_append_paged(self, qkv, in_f32: bool, q_rot: Slice, table: Slice, table_start: int,
+                          positions: Slice, seq_ids: Slice, cache: PagedCache, n: int) -> None:
+        q, k, v = qkv
+        check(lib().cc_batch_rope_append_paged(self._h, q, k, v, int(in_f32), q_rot, table, table_start,
+                                               positions, seq_ids, byref(cache), n))
+
+    def attention_decode_paged(self, q_rot: Slice, cache: PagedCache, seq_lens: Slice, seqs: int,
+                               max_seq_len: int, sinks, window: int, scale: float, out: Slice) -> None:
+        check(lib().cc_batch_attention_decode_paged(self._h, q_rot, byref(cache), seq_lens, seqs,
+                                                    max_seq_len, _opt(sinks), window, scale, out))
+
+    def attention_prefill_paged(self, q_rot: Slice, cache: PagedCache, q_offsets: Slice, starts: Slice,
+                                seqs: int, total_tokens: int, max_t: int, sinks, window: int,
+                                scale: float, out: Slice) -> None:
+        check(lib().cc_batch_attention_prefill_paged(self._h, q_rot, byref(cache), q_offsets, starts, seqs,
+                                                     total_tokens, max_t, _opt(sinks), window, scale, out))
+
+    def read_back(self, s: Slice) -> None:
+        check(lib().cc_batch_read_back(self._h, s))
+
+    @property
+    def dispatches(self) -> int:
+        return lib().cc_batch_dispatches(self._h)
+
+    def commit(self, callback) -> None:
+        """`Batch::commit` (apple.rs:2202-2239): returns at once; `callback(Completed)` runs on
+        the gpu's completion thread once the GPU is done."""
+        buffers = self._buffers
+
+        def done(_user, status, message, seconds):
+            result = seconds if status == 0 else _ERRORS.get(status, Error)((message or b"").decode())
+            callback(Completed(buffers, result))
+
+        fn = COMPLETION_FN(done)
+        _LIVE_CALLBACKS.append(fn)
+        h, self._h = self._h, None
+        check(lib().cc_batch_commit(h, fn, None))
+
+    def run(self) -> Completed:
+        """Commit and wait (what the reference's tests do with a proactor loop)."""
+        seconds = c_double()
+        h, self._h = self._h, None
+        code = lib().cc_batch_commit_wait(h, byref(seconds))
+        if code != 0:
+            return Completed(self._buffers, _ERRORS.get(code, Error)(lib().cc_last_error().decode()))
+        return Completed(self._buffers, seconds.value)
+
+    def drop(self) -> None:
+        if self._h:
+            lib().cc_batch_drop(self._h)
+            self._h = None
+
+
+_LIVE_CALLBACKS: list = []  # ctypes thunks must outlive the completion thread's call

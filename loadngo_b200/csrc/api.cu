@@ -1,0 +1,1071 @@
+// The C ABI of libcuda_compute.so (declared in include/cuda_compute.h): validation, object
+// lifetime, completion delivery.  Kernels live in the other .cu files; this file never
+// computes attention on the CPU and has no fallback when CUDA is unavailable.
+#include "../../include/cuda_compute.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <functional>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "kernels.cuh"
+#include "legacy.cuh"
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(cc_status code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInvalidDevice)
+        return fail(CC_NO_DEVICE, "%s: %s", what, cudaGetErrorString(e));
+    if (e == cudaErrorMemoryAllocation) return fail(CC_ALLOC, "%s: %s", what, cudaGetErrorString(e));
+    if (e == cudaErrorNoKernelImageForDevice || e == cudaErrorInvalidDeviceFunction)
+        return fail(CC_COMPILE, "%s: %s (this library carries sm_100a code only)", what, cudaGetErrorString(e));
+    return fail(CC_GPU, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define CUDA_TRY(expr)                                   \
+    do {                                                 \
+        cudaError_t e_ = (expr);                         \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #expr); \
+    } while (0)
+
+// ---- tensor maps --------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// The pool as rows of 64 bf16 (128 bytes); a box of `box_rows` rows, 128-byte swizzle.
+int make_pool_map(CUtensorMap *map, const void *pool, uint64_t pool_pages, uint32_t kv_heads, uint32_t box_rows) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return fail(CC_COMPILE, "cuTensorMapEncodeTiled is not available from this driver");
+    if (reinterpret_cast<uintptr_t>(pool) % 128 != 0) return fail(CC_DISPATCH, "pool: address is not 128-byte aligned");
+    const uint64_t rows = pool_pages * kv_heads * cc::kTileRows;
+    if (rows == 0 || rows > 0x7fffffffull) return fail(CC_DISPATCH, "pool: %llu rows do not fit", (unsigned long long)rows);
+    cuuint64_t dims[2] = {cc::kHeadDim, rows};
+    cuuint64_t strides[1] = {cc::kHeadDim * 2};
+    cuuint32_t box[2] = {cc::kHeadDim, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(pool), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CC_DISPATCH, "pool: tensor map rejected (CUresult %d)", static_cast<int>(r));
+    return CC_OK;
+}
+
+uint32_t div_up(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+// Pages a sequence of `max_seq_len` keys can show one query, and the split policy: enough
+// CTAs for several waves over 148 SMs x 3 resident CTAs, splits no shorter than 16 pages.
+uint32_t visible_pages(uint32_t max_seq_len, uint32_t window) {
+    if (max_seq_len == 0) return 1;
+    if (window != 0 && max_seq_len > window) {
+        // any alignment of a window of `window` keys touches at most this many pages
+        return div_up(window + cc::kPageTokens - 1, cc::kPageTokens) + 0;
+    }
+    return div_up(max_seq_len, cc::kPageTokens);
+}
+uint32_t choose_pages_per_split(uint32_t seqs, uint32_t kv_heads, uint32_t pages, uint32_t requested) {
+    if (requested) return requested;
+    const uint64_t total = static_cast<uint64_t>(seqs) * kv_heads * pages;
+    const uint64_t want_ctas = 148ull * 3 * 6;
+    uint64_t pps = (total + want_ctas - 1) / want_ctas;
+    if (pps < 16) pps = 16;
+    if (pps > 256) pps = 256;
+    return static_cast<uint32_t>(pps);
+}
+
+}  // namespace
+
+// =================================================================================================
+// A. status
+// =================================================================================================
+extern "C" const char *cc_last_error(void) { return g_error.c_str(); }
+extern "C" const char *cc_version(void) { return "0.1.0"; }
+
+// =================================================================================================
+// B. YaRN table (host, f64) - gpt-oss/src/config.rs:108-133 and gpt-oss/src/gpu.rs:689-697
+// =================================================================================================
+extern "C" int cc_yarn_inv_freq(const cc_rope_params *p, double *inv_freq, double *scale) {
+    if (!p || !inv_freq || !scale) return fail(CC_DISPATCH, "rope: null argument");
+    if (p->head_dim == 0 || p->head_dim % 2 != 0) return fail(CC_DISPATCH, "rope: head_dim %u is not even", p->head_dim);
+    if (!(p->theta > 1.0) || !(p->factor > 0.0) || !(p->original_context > 0.0))
+        return fail(CC_DISPATCH, "rope: theta, factor and original context must be positive");
+    const double two_pi = 2.0 * 3.14159265358979323846264338327950288;
+    const double dim = static_cast<double>(p->head_dim);
+    auto correction = [&](double rotations) {
+        return dim * log(p->original_context / (rotations * two_pi)) / (2.0 * log(p->theta));
+    };
+    double low = fmax(correction(p->beta_fast), 0.0);
+    double high = fmin(correction(p->beta_slow), dim - 1.0);
+    if (low == high) high += 0.001;
+    for (uint32_t i = 0; i < p->head_dim / 2; ++i) {
+        const double freq = pow(p->theta, 2.0 * static_cast<double>(i) / dim);
+        double ramp = (static_cast<double>(i) - low) / (high - low);
+        ramp = ramp < 0.0 ? 0.0 : (ramp > 1.0 ? 1.0 : ramp);
+        const double extrapolation = 1.0 - ramp;
+        inv_freq[i] = (1.0 / (p->factor * freq)) * (1.0 - extrapolation) + (1.0 / freq) * extrapolation;
+    }
+    *scale = p->factor <= 1.0 ? 1.0 : 0.1 * log(p->factor) + 1.0;
+    return CC_OK;
+}
+
+extern "C" int cc_rope_table(const cc_rope_params *p, uint64_t start, uint64_t rows, float *table) {
+    if (!p || !table) return fail(CC_DISPATCH, "rope: null argument");
+    std::vector<double> inv(p->head_dim / 2 + 1);
+    double scale = 1.0;
+    if (int rc = cc_yarn_inv_freq(p, inv.data(), &scale)) return rc;
+    const uint32_t half = p->head_dim / 2;
+    for (uint64_t r = 0; r < rows; ++r) {
+        for (uint32_t i = 0; i < half; ++i) {
+            const double angle = static_cast<double>(start + r) * inv[i];
+            table[(r * half + i) * 2] = static_cast<float>(cos(angle) * scale);
+            table[(r * half + i) * 2 + 1] = static_cast<float>(sin(angle) * scale);
+        }
+    }
+    return CC_OK;
+}
+
+// =================================================================================================
+// C. raw entries
+// =================================================================================================
+namespace {
+
+int check_heads(const char *what, uint32_t heads, uint32_t kv_heads) {
+    if (kv_heads == 0 || heads != kv_heads * cc::kGroup)
+        return fail(CC_DISPATCH, "%s: %u query heads over %u key/value heads; this path needs 8 per key/value head "
+                                 "of width 64", what, heads, kv_heads);
+    return CC_OK;
+}
+
+int launch_status(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    return CC_OK;
+}
+
+}  // namespace
+
+namespace {
+// Validates and translates; launches nothing.
+int rope_append_prepare(const cc_rope_append_args *a, cc::RopeAppendParams *out) {
+    if (!a) return fail(CC_DISPATCH, "rope_append: null arguments");
+    if (int rc = check_heads("rope_append", a->heads, a->kv_heads)) return rc;
+    if (a->n == 0) return fail(CC_DISPATCH, "rope_append: nothing to do");
+    if (!a->q || !a->k || !a->v || !a->q_hi || !a->table || !a->positions || !a->seq_ids || !a->pool ||
+        !a->block_table)
+        return fail(CC_DISPATCH, "rope_append: null pointer");
+    if (a->max_pages == 0 || a->pool_pages == 0 || a->table_rows == 0)
+        return fail(CC_DISPATCH, "rope_append: empty pool, block table or rotary table");
+    if (a->ring_pages > a->max_pages) return fail(CC_DISPATCH, "rope_append: ring of %u pages in a table of %u",
+                                                  a->ring_pages, a->max_pages);
+    for (const void *ptr : {a->q, a->k, a->v, (const void *)a->q_hi, (const void *)a->q_lo, (const void *)a->pool,
+                            (const void *)a->table})
+        if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(CC_DISPATCH, "rope_append: pointer not 16-byte aligned");
+    cc::RopeAppendParams p{};
+    p.q = a->q; p.k = a->k; p.v = a->v;
+    p.in_f32 = a->in_f32 ? 1 : 0;
+    p.q_hi = static_cast<uint16_t *>(a->q_hi);
+    p.q_lo = static_cast<uint16_t *>(a->q_lo);
+    p.table = a->table;
+    p.table_start = static_cast<int64_t>(a->table_start);
+    p.table_rows = static_cast<int64_t>(a->table_rows);
+    p.positions = a->positions;
+    p.seq_ids = a->seq_ids;
+    p.pool = static_cast<uint16_t *>(a->pool);
+    p.block_table = a->block_table;
+    p.max_pages = a->max_pages;
+    p.ring_pages = a->ring_pages;
+    p.n = a->n; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.pool_pages = a->pool_pages;
+    p.status = a->status;
+    *out = p;
+    return CC_OK;
+}
+}  // namespace
+
+extern "C" int cc_rope_append_paged(void *stream, const cc_rope_append_args *a) {
+    cc::RopeAppendParams p;
+    if (int rc = rope_append_prepare(a, &p)) return rc;
+    cc::launch_rope_append(p, static_cast<cudaStream_t>(stream));
+    return launch_status("rope_append launch");
+}
+
+extern "C" size_t cc_decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_seq_len, uint32_t window,
+                                            uint32_t pages_per_split) {
+    const uint32_t pages = visible_pages(max_seq_len, window);
+    const uint32_t pps = choose_pages_per_split(seqs, kv_heads, pages, pages_per_split);
+    return cc::decode_workspace_bytes(seqs, kv_heads, div_up(pages, pps));
+}
+
+namespace {
+// Validates, builds the tensor map and the kernel arguments; launches nothing.
+int decode_prepare(const cc_decode_args *a, cc::DecodeParams *out) {
+    if (!a) return fail(CC_DISPATCH, "decode: null arguments");
+    if (int rc = check_heads("decode", a->heads, a->kv_heads)) return rc;
+    if (a->seqs == 0 || a->seqs > 65535) return fail(CC_DISPATCH, "decode: %u sequences (1..65535)", a->seqs);
+    if (a->kv_heads > 65535) return fail(CC_DISPATCH, "decode: %u key/value heads", a->kv_heads);
+    if (!a->q_hi || !a->pool || !a->block_table || !a->seq_lens || !a->out || !a->workspace)
+        return fail(CC_DISPATCH, "decode: null pointer");
+    if (a->max_seq_len == 0 || a->max_pages == 0 || a->pool_pages == 0)
+        return fail(CC_DISPATCH, "decode: empty sequence bound, block table or pool");
+    if (a->ring_pages > a->max_pages) return fail(CC_DISPATCH, "decode: ring of %u pages in a table of %u",
+                                                  a->ring_pages, a->max_pages);
+    if (a->ring_pages != 0) {
+        // a ring must hold every visible key: window + the partial pages at both ends
+        const uint32_t need = a->window == 0 ? div_up(a->max_seq_len, cc::kPageTokens)
+                                             : div_up(a->window + cc::kPageTokens - 1, cc::kPageTokens);
+        if (a->ring_pages < need)
+            return fail(CC_DISPATCH, "decode: a ring of %u pages cannot hold the %u pages a query sees", a->ring_pages, need);
+    } else if (div_up(a->max_seq_len, cc::kPageTokens) > a->max_pages) {
+        return fail(CC_DISPATCH, "decode: %u keys need more than %u pages per sequence", a->max_seq_len, a->max_pages);
+    }
+    for (const void *ptr : {a->q_hi, a->q_lo, (const void *)a->out, (const void *)a->workspace})
+        if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(CC_DISPATCH, "decode: pointer not 16-byte aligned");
+    const uint32_t pages = visible_pages(a->max_seq_len, a->window);
+    const uint32_t pps = choose_pages_per_split(a->seqs, a->kv_heads, pages, a->pages_per_split);
+    const uint32_t max_splits = div_up(pages, pps);
+    const size_t need = cc::decode_workspace_bytes(a->seqs, a->kv_heads, max_splits);
+    if (a->workspace_bytes < need)
+        return fail(CC_DISPATCH, "decode: workspace of %zu bytes, need %zu", a->workspace_bytes, need);
+    cc::DecodeParams p{};
+    if (int rc = make_pool_map(&p.pool_map, a->pool, a->pool_pages, a->kv_heads, cc::kTileRows)) return rc;
+    p.q_hi = static_cast<const uint16_t *>(a->q_hi);
+    p.q_lo = static_cast<const uint16_t *>(a->q_lo);
+    p.block_table = a->block_table;
+    p.seq_lens = a->seq_lens;
+    p.sinks = a->sinks;
+    p.out = static_cast<uint16_t *>(a->out);
+    const size_t slots = static_cast<size_t>(a->seqs) * a->kv_heads;
+    size_t partial = slots * max_splits * (cc::kGroup * cc::kHeadDim + cc::kGroup * 2) * sizeof(float);
+    partial = (partial + 255) & ~static_cast<size_t>(255);
+    uint8_t *ws = static_cast<uint8_t *>(a->workspace);
+    p.counters = reinterpret_cast<uint32_t *>(ws);  // counters first: they are what must start at zero
+    const size_t counter_bytes = (slots * sizeof(uint32_t) + 255) & ~static_cast<size_t>(255);
+    p.partial_o = reinterpret_cast<float *>(ws + counter_bytes);
+    p.partial_ml = p.partial_o + slots * max_splits * (cc::kGroup * cc::kHeadDim);
+    p.status = a->status;
+    p.seqs = a->seqs; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.max_pages = a->max_pages; p.ring_pages = a->ring_pages; p.pool_pages = a->pool_pages;
+    p.window = a->window;
+    p.pages_per_split = pps;
+    p.max_splits = max_splits;
+    p.scale_log2e = a->scale * 1.4426950408889634f;
+    *out = p;
+    return CC_OK;
+}
+}  // namespace
+
+extern "C" int cc_attention_decode_paged(void *stream, const cc_decode_args *a) {
+    cc::DecodeParams p;
+    if (int rc = decode_prepare(a, &p)) return rc;
+    cc::launch_decode(p, static_cast<cudaStream_t>(stream));
+    return launch_status("decode launch");
+}
+
+
+extern "C" int cc_attention_prefill_paged(void *, const cc_prefill_args *) {
+    return fail(CC_DISPATCH, "prefill: not built into this library yet");
+}
+
+// =================================================================================================
+// D. Gpu, Buffer, Resident
+// =================================================================================================
+struct cc_buffer {
+    cc_gpu *gpu = nullptr;
+    size_t len = 0;
+    uint8_t *dev = nullptr;
+    uint8_t *host = nullptr;       // pinned mirror, or null for device-only
+    // byte ranges that differ between the two copies (empty when lo >= hi)
+    size_t host_dirty_lo = 0, host_dirty_hi = 0;  // host newer than device
+    size_t dev_dirty_lo = 0, dev_dirty_hi = 0;    // device newer than host
+    std::atomic<bool> in_flight{false};
+};
+
+struct cc_resident {
+    cc_gpu *gpu = nullptr;
+    size_t len = 0;
+    uint8_t *dev = nullptr;
+};
+
+struct Pending {
+    cudaEvent_t begin = nullptr, end = nullptr;
+    std::vector<cc_buffer *> buffers;
+    cc_completion_fn done = nullptr;
+    void *user = nullptr;
+    std::string submit_error;  // a launch that failed at commit time
+    bool stop = false;
+};
+
+struct cc_gpu {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    uint32_t *status_dev = nullptr;
+    uint32_t *status_host = nullptr;  // pinned
+    uint8_t *scratch = nullptr;       // decode workspace, grown on demand
+    size_t scratch_bytes = 0;
+    std::vector<uint8_t *> retired;   // outgrown workspaces: recorded batches may still name them
+    std::thread watcher;
+    std::mutex mu;
+    std::condition_variable cv, idle_cv;
+    std::deque<Pending> queue;
+    size_t outstanding = 0;
+};
+
+namespace {
+
+void mark(size_t &lo, size_t &hi, size_t a, size_t b) {
+    if (lo >= hi) { lo = a; hi = b; } else { lo = a < lo ? a : lo; hi = b > hi ? b : hi; }
+}
+
+const char *status_text(uint32_t s) {
+    switch (s) {
+        case cc::kStatusBadPage: return "a block-table entry points outside the page pool";
+        case cc::kStatusBadTableRow: return "a position lies outside the rotary table";
+        case cc::kStatusWaitTimeout: return "a bounded wait for a shared-memory copy ran out";
+        default: return "unknown device status";
+    }
+}
+
+void watcher_main(cc_gpu *gpu) {
+    cudaSetDevice(gpu->device);
+    for (;;) {
+        Pending job;
+        {
+            std::unique_lock<std::mutex> lock(gpu->mu);
+            gpu->cv.wait(lock, [&] { return !gpu->queue.empty(); });
+            job = std::move(gpu->queue.front());
+            gpu->queue.pop_front();
+        }
+        if (job.stop) return;
+        int status = CC_OK;
+        std::string message = job.submit_error;
+        double seconds = 0.0;
+        cudaError_t e = cudaEventSynchronize(job.end);
+        if (e != cudaSuccess) {
+            status = CC_GPU;
+            message = std::string("batch failed: ") + cudaGetErrorString(e);
+        } else {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, job.begin, job.end) == cudaSuccess) seconds = ms * 1e-3;
+            if (!message.empty()) status = CC_GPU;
+            const uint32_t dev_status = *gpu->status_host;
+            if (dev_status != 0 && status == CC_OK) {
+                status = CC_GPU;
+                message = status_text(dev_status);
+            }
+        }
+        cudaEventDestroy(job.begin);
+        cudaEventDestroy(job.end);
+        for (cc_buffer *b : job.buffers) b->in_flight.store(false, std::memory_order_release);
+        if (job.done) job.done(job.user, status, message.c_str(), seconds);
+        {
+            std::lock_guard<std::mutex> lock(gpu->mu);
+            --gpu->outstanding;
+        }
+        gpu->idle_cv.notify_all();
+    }
+}
+
+}  // namespace
+
+extern "C" int cc_gpu_new(int device, cc_gpu **out) {
+    if (!out) return fail(CC_DISPATCH, "gpu: null output");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(CC_NO_DEVICE, "no CUDA device (%s)", e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= count) return fail(CC_NO_DEVICE, "no CUDA device %d (there are %d)", device, count);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(CC_COMPILE, "device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major,
+                    prop.minor);
+    cc_gpu *gpu = new cc_gpu;
+    gpu->device = device;
+    CUDA_TRY(cudaStreamCreateWithFlags(&gpu->stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaMalloc(&gpu->status_dev, 256));
+    CUDA_TRY(cudaMemset(gpu->status_dev, 0, 256));
+    CUDA_TRY(cudaMallocHost(&gpu->status_host, 256));
+    *gpu->status_host = 0;
+    gpu->watcher = std::thread(watcher_main, gpu);
+    *out = gpu;
+    return CC_OK;
+}
+
+extern "C" int cc_gpu_synchronize(cc_gpu *gpu) {
+    if (!gpu) return fail(CC_DISPATCH, "gpu: null");
+    std::unique_lock<std::mutex> lock(gpu->mu);
+    gpu->idle_cv.wait(lock, [&] { return gpu->outstanding == 0; });
+    lock.unlock();
+    cudaSetDevice(gpu->device);
+    CUDA_TRY(cudaStreamSynchronize(gpu->stream));
+    return CC_OK;
+}
+
+extern "C" void cc_gpu_free(cc_gpu *gpu) {
+    if (!gpu) return;
+    cc_gpu_synchronize(gpu);
+    {
+        std::lock_guard<std::mutex> lock(gpu->mu);
+        Pending stop;
+        stop.stop = true;
+        gpu->queue.push_back(std::move(stop));
+    }
+    gpu->cv.notify_all();
+    gpu->watcher.join();
+    cudaSetDevice(gpu->device);
+    if (gpu->scratch) cudaFree(gpu->scratch);
+    for (uint8_t *old : gpu->retired) cudaFree(old);
+    cudaFree(gpu->status_dev);
+    cudaFreeHost(gpu->status_host);
+    cudaStreamDestroy(gpu->stream);
+    delete gpu;
+}
+
+extern "C" void *cc_gpu_stream(cc_gpu *gpu) { return gpu ? gpu->stream : nullptr; }
+
+namespace {
+int buffer_new(cc_gpu *gpu, size_t len, bool mirror, cc_buffer **out) {
+    if (!gpu || !out) return fail(CC_DISPATCH, "buffer: null argument");
+    if (len == 0) return fail(CC_ALLOC, "could not allocate a 0-byte buffer");
+    cudaSetDevice(gpu->device);
+    cc_buffer *b = new cc_buffer;
+    b->gpu = gpu;
+    b->len = len;
+    if (cudaMalloc(&b->dev, len) != cudaSuccess) {
+        cudaGetLastError();
+        delete b;
+        return fail(CC_ALLOC, "could not allocate a %zu-byte device buffer", len);
+    }
+    if (mirror && cudaMallocHost(&b->host, len) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(b->dev);
+        delete b;
+        return fail(CC_ALLOC, "could not allocate a %zu-byte pinned host mirror", len);
+    }
+    *out = b;
+    return CC_OK;
+}
+}  // namespace
+
+extern "C" int cc_buffer_new(cc_gpu *gpu, size_t len, cc_buffer **out) { return buffer_new(gpu, len, true, out); }
+extern "C" int cc_buffer_new_device(cc_gpu *gpu, size_t len, cc_buffer **out) { return buffer_new(gpu, len, false, out); }
+
+extern "C" void cc_buffer_free(cc_buffer *b) {
+    if (!b) return;
+    cudaSetDevice(b->gpu->device);
+    cudaFree(b->dev);
+    if (b->host) cudaFreeHost(b->host);
+    delete b;
+}
+extern "C" size_t cc_buffer_len(const cc_buffer *b) { return b ? b->len : 0; }
+extern "C" void *cc_buffer_device_ptr(cc_buffer *b) { return b ? b->dev : nullptr; }
+
+namespace {
+// Brings the host mirror up to date.  The caller holds the buffer (no batch owns it).
+bool sync_to_host(cc_buffer *b) {
+    if (b->dev_dirty_lo < b->dev_dirty_hi) {
+        cudaSetDevice(b->gpu->device);
+        cudaError_t e = cudaMemcpyAsync(b->host + b->dev_dirty_lo, b->dev + b->dev_dirty_lo,
+                                        b->dev_dirty_hi - b->dev_dirty_lo, cudaMemcpyDeviceToHost, b->gpu->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(b->gpu->stream);
+        if (e != cudaSuccess) {
+            cuda_fail(e, "buffer read-back");
+            return false;
+        }
+        b->dev_dirty_lo = b->dev_dirty_hi = 0;
+    }
+    return true;
+}
+}  // namespace
+
+extern "C" const void *cc_buffer_as_bytes(cc_buffer *b) {
+    if (!b || !b->host) { fail(CC_DISPATCH, "buffer: no host view"); return nullptr; }
+    if (b->in_flight.load(std::memory_order_acquire)) { fail(CC_DISPATCH, "buffer: a batch owns it"); return nullptr; }
+    return sync_to_host(b) ? b->host : nullptr;
+}
+extern "C" void *cc_buffer_write_range(cc_buffer *b, size_t offset, size_t len) {
+    if (!b || !b->host) { fail(CC_DISPATCH, "buffer: no host view"); return nullptr; }
+    if (b->in_flight.load(std::memory_order_acquire)) { fail(CC_DISPATCH, "buffer: a batch owns it"); return nullptr; }
+    if (offset > b->len || len > b->len - offset) { fail(CC_DISPATCH, "buffer: range outside it"); return nullptr; }
+    if (!sync_to_host(b)) return nullptr;
+    if (len) mark(b->host_dirty_lo, b->host_dirty_hi, offset, offset + len);
+    return b->host + offset;
+}
+extern "C" void *cc_buffer_as_bytes_mut(cc_buffer *b) { return b ? cc_buffer_write_range(b, 0, b->len) : nullptr; }
+
+extern "C" int cc_buffer_zero(cc_buffer *b) {
+    if (!b) return fail(CC_DISPATCH, "buffer: null");
+    if (b->in_flight.load(std::memory_order_acquire)) return fail(CC_DISPATCH, "buffer: a batch owns it");
+    cudaSetDevice(b->gpu->device);
+    CUDA_TRY(cudaMemsetAsync(b->dev, 0, b->len, b->gpu->stream));
+    CUDA_TRY(cudaStreamSynchronize(b->gpu->stream));
+    if (b->host) memset(b->host, 0, b->len);
+    b->host_dirty_lo = b->host_dirty_hi = b->dev_dirty_lo = b->dev_dirty_hi = 0;
+    return CC_OK;
+}
+
+extern "C" int cc_resident_new(cc_gpu *gpu, const void *bytes, size_t len, cc_resident **out) {
+    if (!gpu || !bytes || !out) return fail(CC_DISPATCH, "resident: null argument");
+    if (len == 0) return fail(CC_ALLOC, "could not allocate a 0-byte buffer");
+    cudaSetDevice(gpu->device);
+    cc_resident *r = new cc_resident;
+    r->gpu = gpu;
+    r->len = len;
+    if (cudaMalloc(&r->dev, (len + 255) & ~static_cast<size_t>(255)) != cudaSuccess) {
+        cudaGetLastError();
+        delete r;
+        return fail(CC_ALLOC, "could not allocate a %zu-byte resident", len);
+    }
+    cudaError_t e = cudaMemcpy(r->dev, bytes, len, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(r->dev);
+        delete r;
+        return cuda_fail(e, "resident upload");
+    }
+    *out = r;
+    return CC_OK;
+}
+extern "C" void cc_resident_free(cc_resident *r) {
+    if (!r) return;
+    cudaSetDevice(r->gpu->device);
+    cudaFree(r->dev);
+    delete r;
+}
+extern "C" size_t cc_resident_len(const cc_resident *r) { return r ? r->len : 0; }
+
+// =================================================================================================
+// E. Batch: records validated dispatches, launches them all at commit
+// =================================================================================================
+struct cc_batch {
+    cc_gpu *gpu = nullptr;
+    std::vector<cc_buffer *> buffers;
+    std::vector<cc_resident *> residents;
+    std::vector<std::function<int(cudaStream_t)>> work;
+    std::vector<cc_slice> read_backs;
+    std::vector<cc_slice> outputs;  // ranges the recorded work writes; marked device-newer at commit
+    uint32_t dispatches = 0;
+};
+
+namespace {
+
+struct Span {
+    uint8_t *dev;
+    size_t len;
+};
+
+// `Batch::check` (metal-compute/src/apple.rs:860-887): the buffer exists, the slice is exactly
+// `len` bytes, lies inside the buffer, and starts on an `align` boundary.
+int check(const cc_batch *b, const char *what, const cc_slice &s, uint64_t len, uint64_t align, uint8_t **dev) {
+    const size_t total = b->buffers.size() + b->residents.size();
+    if (s.buffer >= total) return fail(CC_DISPATCH, "%s: no buffer %u (batch has %zu)", what, s.buffer, total);
+    const bool resident = s.buffer >= b->buffers.size();
+    const size_t buffer_len = resident ? b->residents[s.buffer - b->buffers.size()]->len : b->buffers[s.buffer]->len;
+    uint8_t *base = resident ? b->residents[s.buffer - b->buffers.size()]->dev : b->buffers[s.buffer]->dev;
+    if (s.len != len)
+        return fail(CC_DISPATCH, "%s: %llu bytes, the shape needs %llu", what, (unsigned long long)s.len,
+                    (unsigned long long)len);
+    if (s.offset > buffer_len || s.len > buffer_len - s.offset)
+        return fail(CC_DISPATCH, "%s: bytes %llu..%llu outside a %zu-byte buffer", what, (unsigned long long)s.offset,
+                    (unsigned long long)(s.offset + s.len), buffer_len);
+    if (s.offset % align != 0)
+        return fail(CC_DISPATCH, "%s: offset %llu is not a multiple of %llu", what, (unsigned long long)s.offset,
+                    (unsigned long long)align);
+    *dev = base + s.offset;
+    return CC_OK;
+}
+
+bool overlaps(const cc_slice &a, const cc_slice &b) {
+    return a.buffer == b.buffer && a.offset < b.offset + b.len && b.offset < a.offset + a.len;
+}
+
+// `Batch::check_output` (apple.rs:896-906).
+int check_output(const cc_batch *b, const cc_slice &y, std::initializer_list<const cc_slice *> inputs) {
+    if (y.buffer >= b->buffers.size()) return fail(CC_DISPATCH, "output is in read-only resident memory");
+    for (const cc_slice *in : inputs)
+        if (in && overlaps(y, *in)) return fail(CC_DISPATCH, "output overlaps an input");
+    return CC_OK;
+}
+
+int narrow(uint64_t n, uint32_t *out) {
+    if (n > 0xffffffffull) return fail(CC_DISPATCH, "%llu does not fit in u32", (unsigned long long)n);
+    *out = static_cast<uint32_t>(n);
+    return CC_OK;
+}
+
+void wrote(cc_batch *b, const cc_slice &s) { b->outputs.push_back(s); }
+
+}  // namespace
+
+extern "C" int cc_batch_begin(cc_gpu *gpu, cc_buffer *const *buffers, uint32_t count, int dispatch, cc_batch **out) {
+    if (!gpu || !out || (count && !buffers)) return fail(CC_DISPATCH, "batch: null argument");
+    if (dispatch != CC_DISPATCH_SERIAL && dispatch != CC_DISPATCH_CONCURRENT)
+        return fail(CC_DISPATCH, "batch: unknown dispatch mode %d", dispatch);
+    for (uint32_t i = 0; i < count; ++i) {
+        if (!buffers[i] || buffers[i]->gpu != gpu) return fail(CC_DISPATCH, "batch: buffer %u is not this gpu's", i);
+        if (buffers[i]->in_flight.load(std::memory_order_acquire))
+            return fail(CC_DISPATCH, "batch: buffer %u belongs to another batch", i);
+        for (uint32_t j = 0; j < i; ++j)
+            if (buffers[j] == buffers[i]) return fail(CC_DISPATCH, "batch: buffer %u given twice", i);
+    }
+    cc_batch *b = new cc_batch;
+    b->gpu = gpu;
+    b->buffers.assign(buffers, buffers + count);
+    for (cc_buffer *buf : b->buffers) buf->in_flight.store(true, std::memory_order_release);
+    *out = b;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_attach(cc_batch *b, cc_resident *r, cc_slice *out) {
+    if (!b || !r || !out) return fail(CC_DISPATCH, "attach: null argument");
+    if (r->gpu != b->gpu) return fail(CC_DISPATCH, "attach: resident of another gpu");
+    size_t index = 0;
+    for (; index < b->residents.size(); ++index)
+        if (b->residents[index] == r) break;
+    if (index == b->residents.size()) b->residents.push_back(r);
+    out->buffer = static_cast<uint32_t>(b->buffers.size() + index);
+    out->offset = 0;
+    out->len = r->len;
+    return CC_OK;
+}
+
+extern "C" uint32_t cc_batch_dispatches(const cc_batch *b) { return b ? b->dispatches : 0; }
+
+extern "C" int cc_batch_barrier(cc_batch *b) {
+    if (!b) return fail(CC_DISPATCH, "barrier: null batch");
+    return CC_OK;  // every dispatch of a batch runs in stream order
+}
+
+extern "C" int cc_batch_copy_rows(cc_batch *b, cc_slice src, uint64_t src_stride, cc_slice dst, uint64_t dst_stride,
+                                  uint64_t rows, uint64_t width) {
+    if (!b) return fail(CC_DISPATCH, "copy_rows: null batch");
+    if (rows == 0 || width == 0 || src_stride < width || dst_stride < width)
+        return fail(CC_DISPATCH, "unsupported copy: %llu x %llu, strides %llu and %llu", (unsigned long long)rows,
+                    (unsigned long long)width, (unsigned long long)src_stride, (unsigned long long)dst_stride);
+    uint32_t r, w, ss, ds, tmp;
+    if (narrow(rows, &r) || narrow(width, &w) || narrow(src_stride, &ss) || narrow(dst_stride, &ds) ||
+        narrow(rows * (src_stride > dst_stride ? src_stride : dst_stride), &tmp))
+        return CC_DISPATCH;
+    uint8_t *ps, *pd;
+    if (int rc = check(b, "src", src, ((rows - 1) * src_stride + width) * 4, 4, &ps)) return rc;
+    if (int rc = check(b, "dst", dst, ((rows - 1) * dst_stride + width) * 4, 4, &pd)) return rc;
+    if (int rc = check_output(b, dst, {&src})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_copy_rows(reinterpret_cast<const float *>(ps), reinterpret_cast<float *>(pd), r, w, ss, ds, s);
+        return CC_OK;
+    });
+    wrote(b, dst);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_rmsnorm_rows(cc_batch *b, cc_slice v, cc_slice w, uint64_t rows, uint64_t d, uint64_t stride,
+                                     float eps) {
+    if (!b) return fail(CC_DISPATCH, "rmsnorm_rows: null batch");
+    if (rows == 0 || d == 0 || stride < d)
+        return fail(CC_DISPATCH, "unsupported rows: %llu x %llu, stride %llu", (unsigned long long)rows,
+                    (unsigned long long)d, (unsigned long long)stride);
+    uint32_t r, dd, st, tmp;
+    if (narrow(rows, &r) || narrow(d, &dd) || narrow(stride, &st) || narrow(rows * stride, &tmp)) return CC_DISPATCH;
+    uint8_t *pv, *pw;
+    if (int rc = check(b, "v", v, ((rows - 1) * stride + d) * 4, 4, &pv)) return rc;
+    if (int rc = check(b, "w", w, d * 4, 4, &pw)) return rc;
+    if (int rc = check_output(b, v, {&w})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_rmsnorm_rows(reinterpret_cast<float *>(pv), reinterpret_cast<const float *>(pw), r, dd, st, eps, s);
+        return CC_OK;
+    });
+    wrote(b, v);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_add_rows(cc_batch *b, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
+                                 uint64_t width) {
+    if (!b) return fail(CC_DISPATCH, "add_rows: null batch");
+    if (rows == 0 || width == 0 || (src_stride != 0 && src_stride < width))
+        return fail(CC_DISPATCH, "unsupported add: %llu x %llu, source stride %llu", (unsigned long long)rows,
+                    (unsigned long long)width, (unsigned long long)src_stride);
+    uint32_t r, w, ss, tmp;
+    if (narrow(rows, &r) || narrow(width, &w) || narrow(src_stride, &ss) || narrow(rows * width, &tmp)) return CC_DISPATCH;
+    uint8_t *pd, *ps;
+    if (int rc = check(b, "dst", dst, rows * width * 4, 4, &pd)) return rc;
+    if (int rc = check(b, "src", src, ((rows - 1) * src_stride + width) * 4, 4, &ps)) return rc;
+    if (int rc = check_output(b, dst, {&src})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_add_rows(reinterpret_cast<float *>(pd), reinterpret_cast<const float *>(ps), r, w, ss, s);
+        return CC_OK;
+    });
+    wrote(b, dst);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_rotate_halves(cc_batch *b, cc_slice x, cc_slice table, uint64_t rows, uint64_t heads,
+                                      uint64_t dim) {
+    if (!b) return fail(CC_DISPATCH, "rotate_halves: null batch");
+    const uint64_t rotary = dim;
+    if (rows == 0 || heads == 0 || rotary == 0 || rotary % 2 != 0)
+        return fail(CC_DISPATCH, "unsupported rotation: %llu rows of %llu x %llu, %llu rotated", (unsigned long long)rows,
+                    (unsigned long long)heads, (unsigned long long)dim, (unsigned long long)rotary);
+    uint32_t r, h, d, tmp;
+    if (narrow(rows, &r) || narrow(heads, &h) || narrow(dim, &d) || narrow(rows * heads * dim, &tmp)) return CC_DISPATCH;
+    uint8_t *px, *pt;
+    if (int rc = check(b, "x", x, rows * heads * dim * 4, 4, &px)) return rc;
+    if (int rc = check(b, "table", table, rows * rotary * 4, 8, &pt)) return rc;
+    if (int rc = check_output(b, x, {&table})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_rotate_halves(reinterpret_cast<float *>(px), reinterpret_cast<const float *>(pt), r, h, d, d, s);
+        return CC_OK;
+    });
+    wrote(b, x);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+namespace {
+
+uint64_t round_up(uint64_t n, uint64_t m) { return (n + m - 1) / m * m; }
+
+// Shared by the plain and the prompt-pass entry (apple.rs:1223-1289 and 1334-1401): the two
+// differ in the shapes they accept and in how many rows the slices must hold.
+int grouped(cc_batch *b, cc_slice q, cc_slice k, cc_slice v, const cc_slice *sinks, cc_slice out,
+            const cc_grouped_shape *shape, bool tiled) {
+    if (!b || !shape) return fail(CC_DISPATCH, "attention_grouped: null argument");
+    const cc_grouped_shape s = *shape;
+    const uint64_t end = s.start + s.t;
+    const uint64_t window_plus_t = s.window > UINT64_MAX - s.t ? UINT64_MAX : s.window + s.t;  // saturating_add
+    const bool ring = s.slots < end;
+    bool bad = s.t == 0 || s.kv_heads == 0 || s.heads % (s.kv_heads ? s.kv_heads : 1) != 0 || s.dim == 0 ||
+               s.dim > 512 || s.window == 0 || s.slots == 0;
+    if (!tiled) bad = bad || s.dim % 32 != 0 || (s.slots < end && s.slots < window_plus_t);
+    // The prompt-pass kernel here walks keys the same way as the plain one, so it needs the
+    // plain one's width rule too; every shape the reference's callers use satisfies both.
+    if (tiled) bad = bad || s.dim % 16 != 0 || s.dim % 32 != 0 || (ring && (s.slots % 32 != 0 || s.slots < window_plus_t));
+    if (bad)
+        return fail(CC_DISPATCH,
+                    "unsupported %sgrouped attention shape {t %llu, start %llu, heads %llu, kv_heads %llu, dim %llu, "
+                    "window %llu, slots %llu}", tiled ? "tiled " : "", (unsigned long long)s.t,
+                    (unsigned long long)s.start, (unsigned long long)s.heads, (unsigned long long)s.kv_heads,
+                    (unsigned long long)s.dim, (unsigned long long)s.window, (unsigned long long)s.slots);
+    cc::GroupedArgs a{};
+    uint32_t groups;
+    if (narrow(s.t, &a.t) || narrow(s.start, &a.start) || narrow(s.heads, &a.heads) || narrow(s.kv_heads, &a.kv_heads) ||
+        narrow(s.dim, &a.dim) || narrow(s.window < end ? s.window : end, &a.window) || narrow(s.slots, &a.slots) ||
+        narrow(end, &groups) || narrow(s.t * s.heads, &groups))
+        return CC_DISPATCH;
+    a.scale = s.scale;
+    a.sinks = sinks ? 1u : 0u;
+    const uint64_t q_rows = tiled ? round_up(s.t, 32) : s.t;
+    const uint64_t kv_rows = tiled ? (ring ? s.slots : round_up(end, 32)) : (s.slots < end ? s.slots : end);
+    uint8_t *pq, *pk, *pv, *po, *ps = nullptr;
+    if (int rc = check(b, "q", q, q_rows * s.heads * s.dim * 4, 4, &pq)) return rc;
+    if (int rc = check(b, "k", k, kv_rows * s.kv_heads * s.dim * 4, 4, &pk)) return rc;
+    if (int rc = check(b, "v", v, kv_rows * s.kv_heads * s.dim * 4, 4, &pv)) return rc;
+    if (int rc = check(b, "out", out, q_rows * s.heads * s.dim * 4, 4, &po)) return rc;
+    if (int rc = check_output(b, out, {&q, &k, &v})) return rc;
+    if (sinks)
+        if (int rc = check(b, "sinks", *sinks, s.heads * 4, 4, &ps)) return rc;
+    b->work.push_back([=](cudaStream_t st) {
+        cc::launch_attention_grouped(reinterpret_cast<const float *>(pq), reinterpret_cast<const float *>(pk),
+                                     reinterpret_cast<const float *>(pv), reinterpret_cast<float *>(po),
+                                     reinterpret_cast<const float *>(ps), a, st);
+        return CC_OK;
+    });
+    wrote(b, out);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+}  // namespace
+
+extern "C" int cc_batch_attention_grouped(cc_batch *b, cc_slice q, cc_slice k, cc_slice v, const cc_slice *sinks,
+                                          cc_slice out, const cc_grouped_shape *shape) {
+    return grouped(b, q, k, v, sinks, out, shape, false);
+}
+extern "C" int cc_batch_attention_grouped_tiled(cc_batch *b, cc_slice q, cc_slice k, cc_slice v,
+                                                const cc_slice *sinks, cc_slice out, const cc_grouped_shape *shape) {
+    return grouped(b, q, k, v, sinks, out, shape, true);
+}
+
+// ---- the paged bf16 path on slices ----------------------------------------------------------------
+namespace {
+int check_cache(cc_batch *b, const cc_paged_cache *c, uint32_t seqs_at_least, uint8_t **pool, uint32_t *pool_pages,
+                uint8_t **table, uint32_t *seqs) {
+    if (!c) return fail(CC_DISPATCH, "cache: null");
+    if (c->kv_heads == 0 || c->max_pages == 0) return fail(CC_DISPATCH, "cache: no key/value heads or pages");
+    const uint64_t tile = static_cast<uint64_t>(c->kv_heads) * cc::kTileBytes;
+    if (c->pool.len == 0 || c->pool.len % tile != 0)
+        return fail(CC_DISPATCH, "pool: %llu bytes is not a whole number of %llu-byte pages", (unsigned long long)c->pool.len,
+                    (unsigned long long)tile);
+    if (int rc = check(b, "pool", c->pool, c->pool.len, 128, pool)) return rc;
+    if (c->pool.buffer >= b->buffers.size()) return fail(CC_DISPATCH, "pool is in read-only resident memory");
+    if (narrow(c->pool.len / tile, pool_pages)) return CC_DISPATCH;
+    const uint64_t row = static_cast<uint64_t>(c->max_pages) * 4;
+    if (c->block_table.len == 0 || c->block_table.len % row != 0)
+        return fail(CC_DISPATCH, "block_table: %llu bytes is not rows of %u pages", (unsigned long long)c->block_table.len,
+                    c->max_pages);
+    if (int rc = check(b, "block_table", c->block_table, c->block_table.len, 4, table)) return rc;
+    if (narrow(c->block_table.len / row, seqs)) return CC_DISPATCH;
+    if (*seqs < seqs_at_least) return fail(CC_DISPATCH, "block_table: %u rows for %u sequences", *seqs, seqs_at_least);
+    return CC_OK;
+}
+}  // namespace
+
+extern "C" int cc_batch_rope_append_paged(cc_batch *b, cc_slice q, cc_slice k, cc_slice v, uint32_t in_f32,
+                                          cc_slice q_rot, cc_slice table, uint64_t table_start, cc_slice positions,
+                                          cc_slice seq_ids, const cc_paged_cache *cache, uint32_t n) {
+    if (!b) return fail(CC_DISPATCH, "rope_append: null batch");
+    if (n == 0) return fail(CC_DISPATCH, "rope_append: nothing to do");
+    uint8_t *pool, *bt;
+    uint32_t pool_pages, seqs;
+    if (int rc = check_cache(b, cache, 1, &pool, &pool_pages, &bt, &seqs)) return rc;
+    const uint64_t heads = static_cast<uint64_t>(cache->kv_heads) * cc::kGroup;
+    const uint64_t esz = in_f32 ? 4 : 2;
+    uint8_t *pq, *pk, *pv, *pr, *pt, *pp, *ps;
+    if (int rc = check(b, "q", q, n * heads * 64 * esz, 16, &pq)) return rc;
+    if (int rc = check(b, "k", k, static_cast<uint64_t>(n) * cache->kv_heads * 64 * esz, 16, &pk)) return rc;
+    if (int rc = check(b, "v", v, static_cast<uint64_t>(n) * cache->kv_heads * 64 * esz, 16, &pv)) return rc;
+    if (int rc = check(b, "q_rot", q_rot, 2 * n * heads * 64 * 2, 16, &pr)) return rc;
+    if (table.len == 0 || table.len % 256 != 0) return fail(CC_DISPATCH, "table: %llu bytes is not rows of 32 pairs",
+                                                            (unsigned long long)table.len);
+    if (int rc = check(b, "table", table, table.len, 16, &pt)) return rc;
+    if (int rc = check(b, "positions", positions, static_cast<uint64_t>(n) * 4, 4, &pp)) return rc;
+    if (int rc = check(b, "seq_ids", seq_ids, static_cast<uint64_t>(n) * 4, 4, &ps)) return rc;
+    if (int rc = check_output(b, q_rot, {&q, &k, &v, &table, &positions, &seq_ids, &cache->block_table})) return rc;
+    if (int rc = check_output(b, cache->pool, {&q, &k, &v, &table, &positions, &seq_ids, &cache->block_table, &q_rot}))
+        return rc;
+    cc_rope_append_args a{};
+    a.q = pq; a.k = pk; a.v = pv; a.in_f32 = in_f32;
+    a.q_hi = pr;
+    a.q_lo = pr + n * heads * 64 * 2;
+    a.table = reinterpret_cast<const float *>(pt);
+    a.table_start = table_start;
+    a.table_rows = table.len / 256;
+    a.positions = reinterpret_cast<const int32_t *>(pp);
+    a.seq_ids = reinterpret_cast<const int32_t *>(ps);
+    a.pool = pool; a.pool_pages = pool_pages;
+    a.block_table = reinterpret_cast<const int32_t *>(bt);
+    a.max_pages = cache->max_pages; a.ring_pages = cache->ring_pages;
+    a.n = n; a.heads = static_cast<uint32_t>(heads); a.kv_heads = cache->kv_heads;
+    a.status = b->gpu->status_dev;
+    cc::RopeAppendParams p;
+    if (int rc = rope_append_prepare(&a, &p)) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_rope_append(p, s);
+        return launch_status("rope_append launch");
+    });
+    wrote(b, q_rot);
+    if (b->buffers[cache->pool.buffer]->host) wrote(b, cache->pool);  // a mirrored pool is read back lazily, whole
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_attention_decode_paged(cc_batch *b, cc_slice q_rot, const cc_paged_cache *cache,
+                                               cc_slice seq_lens, uint32_t seqs, uint32_t max_seq_len,
+                                               const cc_slice *sinks, uint32_t window, float scale, cc_slice out) {
+    if (!b) return fail(CC_DISPATCH, "decode: null batch");
+    if (seqs == 0) return fail(CC_DISPATCH, "decode: nothing to do");
+    uint8_t *pool, *bt;
+    uint32_t pool_pages, rows;
+    if (int rc = check_cache(b, cache, seqs, &pool, &pool_pages, &bt, &rows)) return rc;
+    const uint64_t heads = static_cast<uint64_t>(cache->kv_heads) * cc::kGroup;
+    uint8_t *pr, *pl, *po, *ps = nullptr;
+    if (int rc = check(b, "q_rot", q_rot, 2 * seqs * heads * 64 * 2, 16, &pr)) return rc;
+    if (int rc = check(b, "seq_lens", seq_lens, static_cast<uint64_t>(seqs) * 4, 4, &pl)) return rc;
+    if (int rc = check(b, "out", out, seqs * heads * 64 * 2, 16, &po)) return rc;
+    if (int rc = check_output(b, out, {&q_rot, &cache->pool, &cache->block_table, &seq_lens, sinks})) return rc;
+    if (sinks)
+        if (int rc = check(b, "sinks", *sinks, heads * 4, 4, &ps)) return rc;
+    cc_decode_args a{};
+    a.q_hi = pr;
+    a.q_lo = pr + seqs * heads * 64 * 2;
+    a.pool = pool; a.pool_pages = pool_pages;
+    a.block_table = reinterpret_cast<const int32_t *>(bt);
+    a.max_pages = cache->max_pages; a.ring_pages = cache->ring_pages;
+    a.seq_lens = reinterpret_cast<const int32_t *>(pl);
+    a.seqs = seqs; a.max_seq_len = max_seq_len;
+    a.sinks = reinterpret_cast<const float *>(ps);
+    a.heads = static_cast<uint32_t>(heads); a.kv_heads = cache->kv_heads;
+    a.window = window; a.scale = scale;
+    a.out = po;
+    a.pages_per_split = 0;
+    a.status = b->gpu->status_dev;
+    // The gpu's scratch grows here, while recording, so that commit itself never allocates.
+    const size_t need = cc_decode_workspace_bytes(seqs, cache->kv_heads, max_seq_len, window, 0);
+    cc_gpu *gpu = b->gpu;
+    if (gpu->scratch_bytes < need) {
+        cudaSetDevice(gpu->device);
+        const size_t grow = need + need / 2;
+        uint8_t *fresh = nullptr;
+        if (cudaMalloc(&fresh, grow) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(CC_ALLOC, "could not allocate %zu bytes of decode scratch", grow);
+        }
+        CUDA_TRY(cudaMemset(fresh, 0, grow));
+        if (gpu->scratch) gpu->retired.push_back(gpu->scratch);
+        gpu->scratch = fresh;
+        gpu->scratch_bytes = grow;
+    }
+    a.workspace = gpu->scratch;
+    a.workspace_bytes = gpu->scratch_bytes;
+    cc::DecodeParams p;
+    if (int rc = decode_prepare(&a, &p)) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_decode(p, s);
+        return launch_status("decode launch");
+    });
+    wrote(b, out);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_attention_prefill_paged(cc_batch *, cc_slice, const cc_paged_cache *, cc_slice, cc_slice,
+                                                uint32_t, uint32_t, uint32_t, const cc_slice *, uint32_t, float,
+                                                cc_slice) {
+    return fail(CC_DISPATCH, "prefill: not built into this library yet");
+}
+
+extern "C" int cc_batch_read_back(cc_batch *b, cc_slice s) {
+    if (!b) return fail(CC_DISPATCH, "read_back: null batch");
+    uint8_t *dev;
+    if (int rc = check(b, "read_back", s, s.len, 1, &dev)) return rc;
+    if (s.buffer >= b->buffers.size()) return fail(CC_DISPATCH, "read_back: resident memory has no host mirror");
+    if (!b->buffers[s.buffer]->host) return fail(CC_DISPATCH, "read_back: the buffer has no host mirror");
+    b->read_backs.push_back(s);
+    return CC_OK;
+}
+
+namespace {
+
+// Uploads what the host changed, runs the recorded work, copies requested ranges back, and
+// queues the completion.  Consumes the batch.
+int submit(cc_batch *b, cc_completion_fn done, void *user) {
+    cc_gpu *gpu = b->gpu;
+    cudaSetDevice(gpu->device);
+    Pending job;
+    job.done = done;
+    job.user = user;
+    job.buffers = b->buffers;
+    cudaError_t e = cudaEventCreate(&job.begin);
+    if (e == cudaSuccess) e = cudaEventCreate(&job.end);
+    if (e != cudaSuccess) {
+        for (cc_buffer *buf : b->buffers) buf->in_flight.store(false, std::memory_order_release);
+        delete b;
+        return cuda_fail(e, "batch events");
+    }
+    cudaStream_t s = gpu->stream;
+    for (cc_buffer *buf : b->buffers) {
+        if (buf->host && buf->host_dirty_lo < buf->host_dirty_hi) {
+            cudaMemcpyAsync(buf->dev + buf->host_dirty_lo, buf->host + buf->host_dirty_lo,
+                            buf->host_dirty_hi - buf->host_dirty_lo, cudaMemcpyHostToDevice, s);
+            buf->host_dirty_lo = buf->host_dirty_hi = 0;
+        }
+    }
+    for (const cc_slice &o : b->outputs) {
+        cc_buffer *buf = b->buffers[o.buffer];
+        mark(buf->dev_dirty_lo, buf->dev_dirty_hi, o.offset, o.offset + o.len);
+    }
+    cudaEventRecord(job.begin, s);
+    for (auto &fn : b->work) {
+        if (fn(s) != CC_OK) {
+            job.submit_error = g_error;
+            break;
+        }
+    }
+    for (const cc_slice &rb : b->read_backs) {
+        cc_buffer *buf = b->buffers[rb.buffer];
+        cudaMemcpyAsync(buf->host + rb.offset, buf->dev + rb.offset, rb.len, cudaMemcpyDeviceToHost, s);
+        // what was copied back is clean again if it covers the whole dirty range
+        if (rb.offset <= buf->dev_dirty_lo && rb.offset + rb.len >= buf->dev_dirty_hi)
+            buf->dev_dirty_lo = buf->dev_dirty_hi = 0;
+    }
+    cudaMemcpyAsync(gpu->status_host, gpu->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+    cudaMemsetAsync(gpu->status_dev, 0, sizeof(uint32_t), s);
+    cudaEventRecord(job.end, s);
+    {
+        std::lock_guard<std::mutex> lock(gpu->mu);
+        ++gpu->outstanding;
+        gpu->queue.push_back(std::move(job));
+    }
+    gpu->cv.notify_all();
+    delete b;
+    return CC_OK;
+}
+
+struct WaitBox {
+    std::mutex mu;
+    std::condition_variable cv;
+    bool ready = false;
+    int status = CC_OK;
+    std::string message;
+    double seconds = 0.0;
+};
+
+void wait_done(void *user, int status, const char *message, double seconds) {
+    WaitBox *box = static_cast<WaitBox *>(user);
+    std::lock_guard<std::mutex> lock(box->mu);
+    box->status = status;
+    box->message = message ? message : "";
+    box->seconds = seconds;
+    box->ready = true;
+    box->cv.notify_all();
+}
+
+}  // namespace
+
+extern "C" int cc_batch_commit(cc_batch *b, cc_completion_fn done, void *user) {
+    if (!b) return fail(CC_DISPATCH, "commit: null batch");
+    return submit(b, done, user);
+}
+
+extern "C" int cc_batch_commit_wait(cc_batch *b, double *gpu_seconds) {
+    if (!b) return fail(CC_DISPATCH, "commit: null batch");
+    WaitBox box;
+    if (int rc = submit(b, wait_done, &box)) return rc;
+    std::unique_lock<std::mutex> lock(box.mu);
+    box.cv.wait(lock, [&] { return box.ready; });
+    if (gpu_seconds) *gpu_seconds = box.seconds;
+    if (box.status != CC_OK) return fail(static_cast<cc_status>(box.status), "%s", box.message.c_str());
+    return CC_OK;
+}
+
+extern "C" void cc_batch_drop(cc_batch *b) {
+    if (!b) return;
+    // Nothing recorded has been launched: a dropped batch never runs (apple.rs:553-561).
+    for (cc_buffer *buf : b->buffers) buf->in_flight.store(false, std::memory_order_release);
+    delete b;
+}

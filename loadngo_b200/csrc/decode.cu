@@ -1,0 +1,298 @@
+// Flash-decoding for gpt-oss attention on sm_100a: one new position per sequence against a
+// paged bf16 KV cache, grouped-query (8 query heads per KV head, head_dim 64), per-head sink
+// logits, full or sliding-window visibility.
+//
+// Replaces loadngo's decode kernel `attention_grouped_narrow`
+// (metal-compute/src/kernels.metal:1944-2032, host entry metal-compute/src/apple.rs:1199-1289)
+// and computes what the CPU reference computes per head (gpt-oss/src/model.rs:441-463):
+// s_p = (q.k_p)*scale; max and denominator include the sink, which carries no value.
+//
+// Shape of the work.  The reference runs one threadgroup per query head and so reads each
+// KV head eight times; here the 8 query heads that share a KV head are one MMA tile, so the
+// cache is read once.  Long sequences are cut into splits of `pages_per_split` pages; a CTA
+// owns one (sequence, KV head, split).  Its 4 warps each stream their own pages (16 keys,
+// one 4 KiB K+V tile) from HBM with TMA into a private 4-stage ring of shared memory
+// (128-byte swizzle), so no warp ever waits for another inside the loop.  QK^T and PV run on
+// mma.sync m16n8k16: the 16 rows are the 8 heads' bf16 "hi" parts and their "lo" remainders,
+// (q = hi + lo, p = hi + lo), which costs nothing - the rows would be padding - and keeps the
+// products at ~16 mantissa bits.  Row max / sum use quad shuffles.  Warps merge in shared
+// memory; splits merge through a small scratch buffer, and the CTA that finishes last for a
+// (sequence, KV head) folds the sink in and writes the bf16 output (no second launch, no
+// waiting: the last arriver is found with one atomic ticket).
+//
+// HBM-bound: algorithmic bytes per (sequence, layer) = 2048 * visible keys (+ q, out).
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace cc {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kStages = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kWarpBytes = kStages * kTileBytes;                     // 16 KiB
+constexpr int kSmemBytes = kWarps * kWarpBytes + 1024 /*align*/ + 256 /*barriers*/;
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+
+__global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_constant__ DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int L = p.seq_lens[b];
+    const size_t out_base = (static_cast<size_t>(b) * p.heads + static_cast<size_t>(g) * kGroup) * kHeadDim;
+    if (L <= 0) {  // nothing visible: defined as zeros
+        if (split == 0) {
+            for (int i = tid; i < kGroup * kHeadDim; i += kThreads) p.out[out_base + i] = 0;
+        }
+        return;
+    }
+    const int first = (p.window != 0 && static_cast<uint32_t>(L) > p.window) ? L - static_cast<int>(p.window) : 0;
+    const int page_lo = first >> 4, page_hi = (L - 1) >> 4;
+    const int npages = page_hi - page_lo + 1;
+    const int pps = static_cast<int>(p.pages_per_split);
+    const int splits = (npages + pps - 1) / pps;
+    if (split >= splits) return;
+    const int p0 = page_lo + split * pps;
+    const int p1 = min(p0 + pps, page_hi + 1);
+    const int count = (p1 - p0 > warp) ? (p1 - p0 - warp + kWarps - 1) / kWarps : 0;  // this warp's pages
+
+    // Shared memory: per warp a ring of 4 KiB tiles (1024-aligned for the 128-byte swizzle).
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t aligned = (raw + 1023u) & ~1023u;
+    uint8_t *tiles = smem_raw + (aligned - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + kWarps * kWarpBytes);
+    uint8_t *my_tiles = tiles + warp * kWarpBytes;
+    uint64_t *my_bars = bars + warp * kStages;
+    const uint32_t my_tiles_u32 = smem_u32(my_tiles);
+
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&my_bars[s], 1);
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    const int32_t *table_row = p.block_table + static_cast<size_t>(b) * p.max_pages;
+    auto issue = [&](int it) {
+        const int lp = p0 + warp + it * kWarps;
+        uint32_t idx = static_cast<uint32_t>(lp);
+        if (p.ring_pages) idx %= p.ring_pages;
+        int32_t page = idx < p.max_pages ? table_row[idx] : -1;
+        if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages) {
+            atomicMax(p.status, kStatusBadPage);
+            page = 0;  // still complete the copy so the pipeline drains; the status marks the result invalid
+        }
+        const int stage = it % kStages;
+        mbar_expect_tx(&my_bars[stage], kTileBytes);
+        tma_load_2d(my_tiles + stage * kTileBytes, &p.pool_map, 0,
+                    (page * static_cast<int>(p.kv_heads) + g) * kTileRows, &my_bars[stage]);
+    };
+    if (lane == 0) {
+        for (int s = 0; s < kStages && s < count; ++s) issue(s);
+    }
+
+    // Query fragments: row r (0-7) = head r "hi", row r + 8 = the same head's "lo".
+    const int hr = lane >> 2, tq = lane & 3;
+    uint32_t qa[4][4];
+    {
+        const size_t qrow = out_base + static_cast<size_t>(hr) * kHeadDim;
+        const uint32_t *qh = reinterpret_cast<const uint32_t *>(p.q_hi + qrow);
+        const uint32_t *ql = p.q_lo ? reinterpret_cast<const uint32_t *>(p.q_lo + qrow) : nullptr;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            qa[ks][0] = qh[ks * 8 + tq];
+            qa[ks][2] = qh[ks * 8 + 4 + tq];
+            qa[ks][1] = ql ? ql[ks * 8 + tq] : 0u;
+            qa[ks][3] = ql ? ql[ks * 8 + 4 + tq] : 0u;
+        }
+    }
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m = neg_inf(), l = 0.f;
+    bool failed = false;
+
+    // ldmatrix lane addressing inside a tile (row stride 128 B, 16-byte chunks XOR row%8).
+    const int mi = lane >> 3, r8 = lane & 7;
+    const int k_row = (mi >> 1) * 8 + r8;                  // K: matrices 0,1 keys 0-7; 2,3 keys 8-15
+    const int k_chunk_off = mi & 1;
+    const int v_row = kPageTokens + (mi & 1) * 8 + r8;     // V: matrices 0,2 keys 0-7; 1,3 keys 8-15
+    const int v_chunk_off = mi >> 1;
+
+    for (int it = 0; it < count; ++it) {
+        const int stage = it % kStages;
+        if (!mbar_wait(&my_bars[stage], (it / kStages) & 1)) {
+            failed = true;
+            break;
+        }
+        const uint32_t tile = my_tiles_u32 + stage * kTileBytes;
+        uint32_t kb[4][4], vb[4][4];
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const int chunk = 2 * ks + k_chunk_off;
+            ldmatrix_x4(tile + k_row * 128 + ((chunk ^ r8) << 4), kb[ks][0], kb[ks][1], kb[ks][2], kb[ks][3]);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int chunk = 2 * c + v_chunk_off;
+            ldmatrix_x4_trans(tile + v_row * 128 + ((chunk ^ r8) << 4), vb[c][0], vb[c][1], vb[c][2], vb[c][3]);
+        }
+        __syncwarp();
+        if (lane == 0 && it + kStages < count) issue(it + kStages);
+
+        // S = Q K^T for 16 keys: rows hi and lo add up to the full-precision dot.
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            mma_bf16_16816(s0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[ks][0], kb[ks][1]);
+            mma_bf16_16816(s1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[ks][2], kb[ks][3]);
+        }
+        const int lp = p0 + warp + it * kWarps;
+        const int key0 = lp * kPageTokens + 2 * tq;  // keys key0, key0+1, key0+8, key0+9
+        float x[4];
+        x[0] = (s0[0] + s0[2]) * p.scale_log2e;
+        x[1] = (s0[1] + s0[3]) * p.scale_log2e;
+        x[2] = (s1[0] + s1[2]) * p.scale_log2e;
+        x[3] = (s1[1] + s1[3]) * p.scale_log2e;
+        if (lp == page_lo || lp == page_hi) {  // only edge pages hold keys outside [first, L)
+            const int kp[4] = {key0, key0 + 1, key0 + 8, key0 + 9};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (kp[e] < first || kp[e] >= L) x[e] = neg_inf();
+        }
+        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m, mx);
+        const float m_use = m_new == neg_inf() ? 0.f : m_new;  // all masked so far: weights become 0
+        const float alpha = ex2(m - m_use);                     // m = -inf gives 0
+        float pr[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pr[e] = ex2(x[e] - m_use);
+        l = l * alpha + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+        if (__any_sync(0xffffffffu, m_new != m)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                o[i][0] *= alpha; o[i][1] *= alpha; o[i][2] *= alpha; o[i][3] *= alpha;
+            }
+        }
+        m = m_new;
+        // P as hi + lo bf16 in rows r and r + 8.
+        const uint32_t ph0 = pack_bf16x2_fast(pr[0], pr[1]), ph1 = pack_bf16x2_fast(pr[2], pr[3]);
+        const uint32_t pl0 = pack_bf16x2_fast(pr[0] - __uint_as_float(ph0 << 16),
+                                              pr[1] - __uint_as_float(ph0 & 0xffff0000u));
+        const uint32_t pl1 = pack_bf16x2_fast(pr[2] - __uint_as_float(ph1 << 16),
+                                              pr[3] - __uint_as_float(ph1 & 0xffff0000u));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            mma_bf16_16816(o[2 * c], ph0, pl0, ph1, pl1, vb[c][0], vb[c][1]);
+            mma_bf16_16816(o[2 * c + 1], ph0, pl0, ph1, pl1, vb[c][2], vb[c][3]);
+        }
+    }
+    if (failed && lane == 0) atomicMax(p.status, kStatusWaitTimeout);
+
+    // ---- merge the 4 warps (each warp's own, now idle, tile region is its mailbox) ---------
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    float *box_o = reinterpret_cast<float *>(my_tiles);            // [8][64]
+    float *box_ml = reinterpret_cast<float *>(my_tiles + 2048);    // [8][2]
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float2 v = make_float2(o[i][0] + o[i][2], o[i][1] + o[i][3]);
+        *reinterpret_cast<float2 *>(box_o + hr * kHeadDim + i * 8 + 2 * tq) = v;
+    }
+    if (tq == 0) {
+        box_ml[hr * 2] = m;
+        box_ml[hr * 2 + 1] = l;
+    }
+    __syncthreads();
+
+    const int hh = tid >> 4, d4 = (tid & 15) * 4;
+    float M = neg_inf();
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, reinterpret_cast<float *>(tiles + w * kWarpBytes + 2048)[hh * 2]);
+    float Ls = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const float *wml = reinterpret_cast<float *>(tiles + w * kWarpBytes + 2048);
+        const float mw = wml[hh * 2];
+        const float a = mw == neg_inf() ? 0.f : ex2(mw - M);
+        Ls += a * wml[hh * 2 + 1];
+        const float4 ov = *reinterpret_cast<const float4 *>(tiles + w * kWarpBytes + (hh * kHeadDim + d4) * 4);
+        acc.x += a * ov.x; acc.y += a * ov.y; acc.z += a * ov.z; acc.w += a * ov.w;
+    }
+
+    const int head = g * kGroup + hh;
+    const float sink2 = p.sinks ? p.sinks[head] * 1.4426950408889634f : neg_inf();
+    auto finish = [&](float Mx, float Lx, float4 Ox) {
+        const float Mt = fmaxf(Mx, sink2);
+        const float e = Mx == neg_inf() ? 0.f : ex2(Mx - Mt);
+        const float total = Lx * e + (p.sinks ? ex2(sink2 - Mt) : 0.f);
+        const float inv = total > 0.f ? e / total : 0.f;
+        uint2 packed = make_uint2(pack_bf16x2(Ox.x * inv, Ox.y * inv), pack_bf16x2(Ox.z * inv, Ox.w * inv));
+        *reinterpret_cast<uint2 *>(p.out + out_base + hh * kHeadDim + d4) = packed;
+    };
+    if (splits == 1) {
+        finish(M, Ls, acc);
+        return;
+    }
+
+    // ---- several splits: park the partial, the last CTA to arrive merges them ---------------
+    const size_t slot = (static_cast<size_t>(b) * p.kv_heads + g) * p.max_splits;
+    float *po = p.partial_o + (slot + split) * (kGroup * kHeadDim);
+    float *pml = p.partial_ml + (slot + split) * (kGroup * 2);
+    __stcg(reinterpret_cast<float4 *>(po + hh * kHeadDim + d4), acc);
+    if ((tid & 15) == 0) __stcg(reinterpret_cast<float2 *>(pml + hh * 2), make_float2(M, Ls));
+    __threadfence();
+    __syncthreads();
+    __shared__ int s_last;
+    if (tid == 0) {
+        const uint32_t ticket = atomicAdd(&p.counters[static_cast<size_t>(b) * p.kv_heads + g], 1u);
+        s_last = ticket == static_cast<uint32_t>(splits - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float Mx = neg_inf(), Lx = 0.f;
+    float4 Ox = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.partial_ml + (slot + s) * (kGroup * 2) + hh * 2));
+        const float4 ov =
+            __ldcg(reinterpret_cast<const float4 *>(p.partial_o + (slot + s) * (kGroup * kHeadDim) + hh * kHeadDim + d4));
+        const float Mn = fmaxf(Mx, ml.x);
+        const float a_old = Mx == neg_inf() ? 0.f : ex2(Mx - Mn);
+        const float a_new = ml.x == neg_inf() ? 0.f : ex2(ml.x - Mn);
+        Lx = Lx * a_old + ml.y * a_new;
+        Ox.x = Ox.x * a_old + ov.x * a_new;
+        Ox.y = Ox.y * a_old + ov.y * a_new;
+        Ox.z = Ox.z * a_old + ov.z * a_new;
+        Ox.w = Ox.w * a_old + ov.w * a_new;
+        Mx = Mn;
+    }
+    finish(Mx, Lx, Ox);
+    if (tid == 0) p.counters[static_cast<size_t>(b) * p.kv_heads + g] = 0;  // ready for the next launch
+}
+
+}  // namespace
+
+size_t decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_splits) {
+    const size_t slots = static_cast<size_t>(seqs) * kv_heads;
+    size_t bytes = slots * max_splits * (kGroup * kHeadDim + kGroup * 2) * sizeof(float);
+    bytes = (bytes + 255) & ~static_cast<size_t>(255);
+    return bytes + ((slots * sizeof(uint32_t) + 255) & ~static_cast<size_t>(255));
+}
+
+void launch_decode(const DecodeParams &p, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        configured = true;
+    }
+    dim3 grid(p.max_splits, p.kv_heads, p.seqs);
+    decode_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+}
+
+}  // namespace cc

@@ -1,0 +1,66 @@
+// Launchers of the sm_100a kernels behind the C ABI (api.cu validates, these only launch).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cc {
+
+// ---- Paged bf16 KV cache geometry -----------------------------------------------------------
+// pool[page][kv_head][2][16][64] bf16: per (page, kv head) one 4 KiB tile, keys in rows 0-15,
+// values in rows 16-31, 128 bytes per row.  Viewed by TMA as a 2-D tensor of 64-wide rows.
+constexpr int kPageTokens = 16;
+constexpr int kHeadDim = 64;
+constexpr int kGroup = 8;                                   // query heads per kv head
+constexpr int kTileRows = 2 * kPageTokens;                  // K rows then V rows
+constexpr int kTileBytes = kTileRows * kHeadDim * 2;        // 4096
+
+struct RopeAppendParams {
+    const void *q, *k, *v;        // [n][heads][64], [n][kv_heads][64] x2; bf16 or f32
+    int in_f32;                   // 0: bf16 inputs, 1: f32 inputs
+    uint16_t *q_hi, *q_lo;        // [n][heads][64] bf16: rotated q = hi + lo (lo may be null)
+    const float *table;           // [table_rows][32][2] (cos, sin), row = position - table_start
+    int64_t table_start;
+    int64_t table_rows;
+    const int32_t *positions;     // [n] absolute position of each token
+    const int32_t *seq_ids;       // [n] block-table row of each token
+    uint16_t *pool;
+    const int32_t *block_table;   // [seqs][max_pages]
+    uint32_t max_pages;
+    uint32_t ring_pages;          // 0: page = block_table[seq][pos/16]; else [(pos/16) % ring_pages]
+    uint32_t n, heads, kv_heads;
+    uint32_t pool_pages;
+    uint32_t *status;             // device error word (0 = ok)
+};
+void launch_rope_append(const RopeAppendParams &p, cudaStream_t stream);
+
+struct DecodeParams {
+    CUtensorMap pool_map;         // rows of 64 bf16, box 64 x 32 (one K+V tile), 128B swizzle
+    const uint16_t *q_hi, *q_lo;  // [seqs][heads][64]
+    const int32_t *block_table;   // [seqs][max_pages]
+    const int32_t *seq_lens;      // [seqs] keys visible to the query, itself included (>= 1)
+    const float *sinks;           // [heads] or null
+    uint16_t *out;                // [seqs][heads][64] bf16
+    float *partial_o;             // [seqs][kv_heads][max_splits][8][64]
+    float *partial_ml;            // [seqs][kv_heads][max_splits][8][2]
+    uint32_t *counters;           // [seqs][kv_heads], zero between launches
+    uint32_t *status;
+    uint32_t seqs, heads, kv_heads, max_pages, ring_pages, pool_pages;
+    uint32_t window;              // 0 = all keys
+    uint32_t pages_per_split, max_splits;
+    float scale_log2e;            // softmax scale * log2(e)
+};
+void launch_decode(const DecodeParams &p, cudaStream_t stream);
+// Bytes of scratch `launch_decode` needs for the given sizes (partials + counters).
+size_t decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_splits);
+
+// Error codes kernels write to the status word.
+enum : uint32_t {
+    kStatusOk = 0,
+    kStatusBadPage = 1,       // a block-table entry outside the pool
+    kStatusBadTableRow = 2,   // a position outside the cos/sin table
+    kStatusWaitTimeout = 3,   // a bounded wait on a copy ran out
+};
+
+}  // namespace cc

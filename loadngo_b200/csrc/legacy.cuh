@@ -1,0 +1,28 @@
+// Launchers of the float32 ring-cache kernels (see legacy.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cc {
+
+// Device-side argument block of grouped attention; the fields of metal-compute's
+// `GroupedArgs` (metal-compute/src/apple.rs:616-627), window already clamped to start + t.
+struct GroupedArgs {
+    uint32_t t, start, heads, kv_heads, dim, window, slots;
+    float scale;
+    uint32_t sinks;
+};
+
+void launch_copy_rows(const float *src, float *dst, uint32_t rows, uint32_t width, uint32_t src_stride,
+                      uint32_t dst_stride, cudaStream_t stream);
+void launch_add_rows(float *dst, const float *src, uint32_t rows, uint32_t width, uint32_t src_stride,
+                     cudaStream_t stream);
+void launch_rmsnorm_rows(float *v, const float *w, uint32_t rows, uint32_t d, uint32_t stride, float eps,
+                         cudaStream_t stream);
+void launch_rotate_halves(float *x, const float *table, uint32_t rows, uint32_t heads, uint32_t dim, uint32_t rotary,
+                          cudaStream_t stream);
+void launch_attention_grouped(const float *q, const float *k, const float *v, float *out, const float *sinks,
+                              const GroupedArgs &a, cudaStream_t stream);
+
+}  // namespace cc

@@ -1,0 +1,260 @@
+/*
+ * CPU oracle for the gpt-oss attention hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C restatement of the arithmetic of loadngo's CPU reference
+ * (`gpt-oss/src/model.rs`, `gpt-oss/src/config.rs`, `weights/src/dtype.rs`,
+ * `weights/src/dense.rs`).  It exists to check the CUDA kernels and to be timed as the
+ * CPU baseline.  Nothing in the shipped library links, loads or calls it: only the test
+ * suite, the smoke check and the benchmark's CPU-baseline leg do.
+ *
+ * Parity pin: the restatement reproduces the reference's own end-to-end fixture
+ * (`gpt-oss/tests/fixtures/tiny`, tolerance 2e-3 as `gpt-oss/tests/tiny_oracle.rs:10`)
+ * when it supplies the attention inside a whole-model replay; the per-layer attention
+ * inputs and outputs of that replay are committed as golden vectors beside the script
+ * that made them.  The bf16 rounding rule is pinned by the known answers of
+ * `weights/src/dtype.rs:182-203`, the grouped attention by the float64 definition of
+ * `metal-compute/tests/attention_grouped.rs:65-100`.
+ *
+ * The one switch the reference does not have is `cache_bf16`: the reference keeps keys
+ * and values as f32 (`model.rs:189-190`, `:432-433`); with `cache_bf16 = 1` the rotated
+ * key and the value are rounded to bfloat16 (round-to-nearest-even) when appended and
+ * nothing else changes.  That is the mode a bf16 KV cache is gated against.
+ *
+ * Build: see the Makefile beside this file (gcc -O2 -ffp-contract=off, so that the f32
+ * sums keep the reference's order and no multiply-add is fused).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <pthread.h>
+#include <unistd.h>
+
+/* ---- bfloat16 (weights/src/dtype.rs:94-110) ---------------------------------------- */
+
+float oracle_bf16_to_f32(uint16_t bits) {
+    uint32_t wide = (uint32_t)bits << 16;
+    float out;
+    memcpy(&out, &wide, 4);
+    return out;
+}
+
+/* Round to nearest, ties to even; a NaN stays a quiet NaN (dtype.rs:102-110). */
+uint16_t oracle_f32_to_bf16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    if (value != value) {
+        return (uint16_t)((bits >> 16) | 0x40);
+    }
+    uint32_t bias = 0x7fffu + ((bits >> 16) & 1u);
+    return (uint16_t)((bits + bias) >> 16);
+}
+
+static float round_bf16(float v) { return oracle_bf16_to_f32(oracle_f32_to_bf16(v)); }
+
+void oracle_round_bf16_array(const float *in, float *out, long n) {
+    for (long i = 0; i < n; ++i) out[i] = round_bf16(in[i]);
+}
+
+/* ---- YaRN (gpt-oss/src/config.rs:108-133; beta constants :30-31) -------------------- */
+
+/* inv_freq: head_dim/2 doubles.  *scale: the factor on every cosine and sine. */
+void oracle_yarn(int head_dim, double theta, double factor, double original_context,
+                 double beta_fast, double beta_slow, double *inv_freq, double *scale) {
+    const double pi = 3.14159265358979323846264338327950288;
+    double dim = (double)head_dim;
+    int half = head_dim / 2;
+    /* correction(rotations) = dim * ln(orig / (rotations * 2 pi)) / (2 ln theta) */
+    double low = dim * log(original_context / (beta_fast * 2.0 * pi)) / (2.0 * log(theta));
+    double high = dim * log(original_context / (beta_slow * 2.0 * pi)) / (2.0 * log(theta));
+    if (low < 0.0) low = 0.0;                 /* .max(0.0) */
+    if (high > dim - 1.0) high = dim - 1.0;   /* .min(dim - 1) */
+    if (low == high) high += 0.001;
+    for (int i = 0; i < half; ++i) {
+        double freq = pow(theta, 2.0 * (double)i / dim);
+        double ramp = ((double)i - low) / (high - low);
+        if (ramp < 0.0) ramp = 0.0;
+        if (ramp > 1.0) ramp = 1.0;
+        double extrapolation = 1.0 - ramp;
+        inv_freq[i] = (1.0 / (factor * freq)) * (1.0 - extrapolation) + (1.0 / freq) * extrapolation;
+    }
+    *scale = factor <= 1.0 ? 1.0 : 0.1 * log(factor) + 1.0;
+}
+
+/* The (cos, sin) table the GPU path uploads: row p holds `half` pairs for position
+ * start + p; angle and factor in f64, then one cast to f32 (gpt-oss/src/gpu.rs:689-697). */
+void oracle_rope_table(const double *inv_freq, double scale, int half, long start, long t,
+                       float *table) {
+    for (long p = 0; p < t; ++p) {
+        for (int i = 0; i < half; ++i) {
+            double angle = (double)(start + p) * inv_freq[i];
+            table[(p * half + i) * 2] = (float)(cos(angle) * scale);
+            table[(p * half + i) * 2 + 1] = (float)(sin(angle) * scale);
+        }
+    }
+}
+
+/* Rotation by halves for one position (gpt-oss/src/model.rs:389-404): element i of the
+ * first half turns with element i of the second, f32 arithmetic, no fused multiply-add. */
+void oracle_rotate(float *x, int heads, int dim, const double *inv_freq, double scale, long pos) {
+    int half = dim / 2;
+    for (int h = 0; h < heads; ++h) {
+        float *head = x + (long)h * dim;
+        for (int i = 0; i < half; ++i) {
+            double angle = (double)pos * inv_freq[i];
+            float c = (float)(cos(angle) * scale);
+            float s = (float)(sin(angle) * scale);
+            float a = head[i], b = head[i + half];
+            head[i] = a * c - b * s;
+            head[i + half] = b * c + a * s;
+        }
+    }
+}
+
+/* ---- one head of one position (gpt-oss/src/model.rs:441-463) ------------------------ */
+
+static void attend_head(const float *query, const float *keys, const float *values, long first,
+                        long pos, int kv_heads, int kv, int dim, float scale, int has_sink,
+                        float sink, float *scores, float *target) {
+    long n = pos + 1 - first;
+    for (long p = first; p <= pos; ++p) {
+        const float *key = keys + (p * kv_heads + kv) * (long)dim;
+        float dot = 0.0f;
+        for (int d = 0; d < dim; ++d) dot += query[d] * key[d];
+        scores[p - first] = dot * scale;
+    }
+    /* The sink joins the maximum and the denominator and carries no value (:449-455).
+     * Without a sink the fold starts from -inf, as the float64 definition in
+     * metal-compute/tests/attention_grouped.rs:86-88 does. */
+    float max = has_sink ? sink : -INFINITY;
+    for (long i = 0; i < n; ++i) max = scores[i] > max ? scores[i] : max;
+    float total = has_sink ? expf(sink - max) : 0.0f;
+    for (long i = 0; i < n; ++i) {
+        scores[i] = expf(scores[i] - max);
+        total += scores[i];
+    }
+    for (int d = 0; d < dim; ++d) target[d] = 0.0f;
+    for (long p = first; p <= pos; ++p) {
+        const float *value = values + (p * kv_heads + kv) * (long)dim;
+        float w = scores[p - first] / total;   /* weight / total * val (:461) */
+        for (int d = 0; d < dim; ++d) target[d] += w * value[d];
+    }
+}
+
+struct attend_job {
+    const float *qr, *kcache, *vcache, *sinks;
+    float *out;
+    long start, t;
+    int heads, kv_heads, dim;
+    long window;
+    float scale;
+    int worker, workers;
+};
+
+/* (position, head) items `worker`, `worker + workers`, ...: each item is the reference's
+ * loop body for one head, so results do not depend on how items are spread. */
+static void *attend_items(void *arg) {
+    const struct attend_job *j = (const struct attend_job *)arg;
+    int group = j->heads / j->kv_heads;
+    long qw = (long)j->heads * j->dim;
+    long rows = j->start + j->t;
+    float *scores = (float *)malloc(sizeof(float) * (size_t)(rows > 0 ? rows : 1));
+    for (long item = j->worker; item < j->t * j->heads; item += j->workers) {
+        long i = item / j->heads;
+        int head = (int)(item % j->heads);
+        long pos = j->start + i;
+        long first = 0;
+        if (j->window > 0) first = pos + 1 > j->window ? pos + 1 - j->window : 0; /* saturating_sub */
+        attend_head(j->qr + i * qw + (long)head * j->dim, j->kcache, j->vcache, first, pos,
+                    j->kv_heads, head / group, j->dim, j->scale, j->sinks != NULL,
+                    j->sinks ? j->sinks[head] : 0.0f, scores, j->out + i * qw + (long)head * j->dim);
+    }
+    free(scores);
+    return NULL;
+}
+
+/*
+ * `t` new positions from absolute position `start`, fed one at a time as the reference
+ * does (gpt-oss/src/engine.rs:166-168 -> model.rs:408): rotate q and k (:430-431), append
+ * k and v to the caches (:432-433), window start (:434-438), every head (:441-463).
+ *
+ *   q [t][heads][dim], k, v [t][kv_heads][dim]: f32, before rotation.
+ *   kcache, vcache [start + t][kv_heads][dim] f32: rows < start already hold the past.
+ *   window: keys a query sees, itself included; <= 0 means all of them.
+ *   sinks: [heads] or NULL.   apply_rope: 0 leaves q and k as given.
+ *   cache_bf16: round the appended rotated key and value to bfloat16 (not in the
+ *   reference; see the header).
+ *   out [t][heads][dim] f32.  q_rot (optional) receives the rotated queries.
+ *   threads: 1 follows the reference (its attention loop is single-threaded); more
+ *   spreads (position, head) pairs over that many pthreads after all appends are done,
+ *   which leaves every result bit-identical.
+ */
+void oracle_attention(const float *q, const float *k, const float *v, float *kcache,
+                      float *vcache, long start, long t, int heads, int kv_heads, int dim,
+                      long window, float scale, const float *sinks, const double *inv_freq,
+                      double rope_scale, int apply_rope, int cache_bf16, float *out, float *q_rot,
+                      int threads) {
+    long qw = (long)heads * dim, kw = (long)kv_heads * dim;
+    float *qr = q_rot ? q_rot : (float *)malloc(sizeof(float) * (size_t)(t * qw));
+    memcpy(qr, q, sizeof(float) * (size_t)(t * qw));
+    for (long i = 0; i < t; ++i) {
+        long pos = start + i;
+        float *krow = kcache + pos * kw, *vrow = vcache + pos * kw;
+        memcpy(krow, k + i * kw, sizeof(float) * (size_t)kw);
+        memcpy(vrow, v + i * kw, sizeof(float) * (size_t)kw);
+        if (apply_rope) {
+            oracle_rotate(qr + i * qw, heads, dim, inv_freq, rope_scale, pos);
+            oracle_rotate(krow, kv_heads, dim, inv_freq, rope_scale, pos);
+        }
+        if (cache_bf16) {
+            for (long j = 0; j < kw; ++j) {
+                krow[j] = round_bf16(krow[j]);
+                vrow[j] = round_bf16(vrow[j]);
+            }
+        }
+    }
+    struct attend_job job = {qr, kcache, vcache, sinks, out, start, t, heads, kv_heads, dim,
+                             window, scale, 0, 1};
+    if (threads <= 1) {
+        attend_items(&job);
+    } else {
+        if (threads > 256) threads = 256;
+        pthread_t ids[256];
+        struct attend_job jobs[256];
+        for (int w = 0; w < threads; ++w) {
+            jobs[w] = job;
+            jobs[w].worker = w;
+            jobs[w].workers = threads;
+            pthread_create(&ids[w], NULL, attend_items, &jobs[w]);
+        }
+        for (int w = 0; w < threads; ++w) pthread_join(ids[w], NULL);
+    }
+    if (!q_rot) free(qr);
+}
+
+/* ---- attention-block glue used by the tensor-parallel block configuration ---------- */
+
+/* x * w / sqrt(mean(x^2) + eps): f64 mean, f32 scale (gpt-oss/src/model.rs:274-280). */
+void oracle_rms_norm(const float *x, const float *weight, float eps, long n, float *out) {
+    double mean = 0.0;
+    for (long i = 0; i < n; ++i) mean += (double)x[i] * (double)x[i];
+    mean /= (double)n;
+    float scale = (float)(1.0 / sqrt(mean + (double)eps));
+    for (long i = 0; i < n; ++i) out[i] = x[i] * scale * weight[i];
+}
+
+/* y = W x for a bfloat16 row-major W, each row summed in f64 in column order, one cast
+ * to f32 (weights/src/dense.rs:82-94). */
+void oracle_bf16_matvec(const uint16_t *w, long rows, long cols, const float *x, float *y) {
+    for (long r = 0; r < rows; ++r) {
+        double acc = 0.0;
+        for (long c = 0; c < cols; ++c) acc += (double)oracle_bf16_to_f32(w[r * cols + c]) * (double)x[c];
+        y[r] = (float)acc;
+    }
+}
+
+int oracle_max_threads(void) {
+    long n = sysconf(_SC_NPROCESSORS_ONLN);
+    return n > 0 ? (int)n : 1;
+}

@@ -1,0 +1,173 @@
+"""ctypes bindings of the C oracle (`oracle.c`).  Test infrastructure only.
+
+The shipped library never imports this module: it is the checker for the CUDA path (tests,
+the smoke check) and the timed CPU baseline of the benchmark.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from dataclasses import dataclass
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
+_lib = None
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+
+
+def build(force: bool = False) -> str:
+    """Compiles `oracle.c` with the Makefile beside it (gcc only)."""
+    src = os.path.join(_HERE, "oracle.c")
+    stale = not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    if force or stale:
+        env = dict(os.environ, CC="gcc")
+        subprocess.run(["make", "-C", _HERE, "-B", "CC=gcc"], check=True, env=env,
+                       stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(_LIB_PATH)
+        L.oracle_bf16_to_f32.restype = ctypes.c_float
+        L.oracle_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        L.oracle_f32_to_bf16.restype = ctypes.c_uint16
+        L.oracle_f32_to_bf16.argtypes = [ctypes.c_float]
+        L.oracle_round_bf16_array.argtypes = [_f32p, _f32p, ctypes.c_long]
+        L.oracle_yarn.argtypes = [ctypes.c_int] + [ctypes.c_double] * 5 + [_f64p, _f64p]
+        L.oracle_rope_table.argtypes = [_f64p, ctypes.c_double, ctypes.c_int, ctypes.c_long,
+                                        ctypes.c_long, _f32p]
+        L.oracle_rotate.argtypes = [_f32p, ctypes.c_int, ctypes.c_int, _f64p, ctypes.c_double,
+                                    ctypes.c_long]
+        L.oracle_attention.argtypes = [
+            _f32p, _f32p, _f32p, _f32p, _f32p, ctypes.c_long, ctypes.c_long, ctypes.c_int,
+            ctypes.c_int, ctypes.c_int, ctypes.c_long, ctypes.c_float, ctypes.c_void_p, _f64p,
+            ctypes.c_double, ctypes.c_int, ctypes.c_int, _f32p, ctypes.c_void_p, ctypes.c_int]
+        L.oracle_rms_norm.argtypes = [_f32p, _f32p, ctypes.c_float, ctypes.c_long, _f32p]
+        L.oracle_bf16_matvec.argtypes = [_u16p, ctypes.c_long, ctypes.c_long, _f32p, _f32p]
+        L.oracle_max_threads.restype = ctypes.c_int
+        _lib = L
+    return _lib
+
+
+@dataclass(frozen=True)
+class Rope:
+    """YaRN parameters; the defaults are gpt-oss's (config.rs:30-31 for the betas)."""
+    head_dim: int = 64
+    theta: float = 150000.0
+    factor: float = 32.0
+    original_context: float = 4096.0
+    beta_fast: float = 32.0
+    beta_slow: float = 1.0
+
+    def inv_freq(self):
+        inv = np.zeros(self.head_dim // 2, np.float64)
+        scale = np.zeros(1, np.float64)
+        lib().oracle_yarn(self.head_dim, self.theta, self.factor, self.original_context,
+                          self.beta_fast, self.beta_slow, inv, scale)
+        return inv, float(scale[0])
+
+    def table(self, start: int, t: int) -> np.ndarray:
+        """[t][half][2] f32 (cos, sin) rows for positions start .. start + t."""
+        inv, scale = self.inv_freq()
+        out = np.zeros((t, self.head_dim // 2, 2), np.float32)
+        lib().oracle_rope_table(inv, scale, self.head_dim // 2, start, t, out)
+        return out
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even bfloat16 bits of an f32 array (weights/src/dtype.rs:102-110),
+    vectorised; `tests` check it against the scalar C function."""
+    x = np.ascontiguousarray(x, np.float32)
+    bits = x.view(np.uint32)
+    bias = np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))
+    out = ((bits + bias) >> np.uint32(16)).astype(np.uint16)
+    nan = np.isnan(x)
+    if nan.any():
+        out[nan] = ((bits[nan] >> np.uint32(16)) | np.uint32(0x40)).astype(np.uint16)
+    return out
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    return bf16_bits_to_f32(f32_to_bf16_bits(x))
+
+
+class Session:
+    """The reference's `Session` for one layer (model.rs:188-214): f32 key and value rows by
+    position, a length, `truncate`.  `cache_bf16` rounds what is appended."""
+
+    def __init__(self, heads: int, kv_heads: int, dim: int, capacity: int, *, window: int = 0,
+                 scale: float | None = None, sinks: np.ndarray | None = None,
+                 rope: Rope | None = None, cache_bf16: bool = False):
+        self.heads, self.kv_heads, self.dim = heads, kv_heads, dim
+        self.window = window
+        self.scale = np.float32(1.0 / np.sqrt(np.float32(dim))) if scale is None else np.float32(scale)
+        self.sinks = None if sinks is None else np.ascontiguousarray(sinks, np.float32)
+        self.rope = rope
+        self.cache_bf16 = cache_bf16
+        self.keys = np.zeros((capacity, kv_heads, dim), np.float32)
+        self.values = np.zeros((capacity, kv_heads, dim), np.float32)
+        self.len = 0
+        if rope is not None:
+            self._inv, self._rope_scale = rope.inv_freq()
+        else:
+            self._inv, self._rope_scale = np.zeros(dim // 2, np.float64), 1.0
+
+    def truncate(self, length: int) -> None:
+        if length < self.len:
+            self.len = length
+
+    def feed(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, threads: int = 1):
+        """Feeds t new positions (q [t][heads][dim], k and v [t][kv_heads][dim], f32, before
+        rotation).  Returns (out [t][heads][dim] f32, rotated q)."""
+        q = np.ascontiguousarray(q, np.float32)
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        t = q.shape[0]
+        assert self.len + t <= self.keys.shape[0], "session capacity"
+        out = np.zeros_like(q)
+        q_rot = np.zeros_like(q)
+        sinks = None if self.sinks is None else self.sinks.ctypes.data_as(ctypes.c_void_p)
+        lib().oracle_attention(q, k, v, self.keys.reshape(-1), self.values.reshape(-1),
+                               self.len, t, self.heads, self.kv_heads, self.dim, self.window,
+                               float(self.scale), sinks, self._inv, self._rope_scale,
+                               int(self.rope is not None), int(self.cache_bf16), out.reshape(-1),
+                               q_rot.ctypes.data_as(ctypes.c_void_p), threads)
+        self.len += t
+        return out, q_rot
+
+
+def attention_f64(q, k, v, *, start, window, scale, sinks=None):
+    """The float64 definition of grouped attention the reference's kernel tests use
+    (metal-compute/tests/attention_grouped.rs:65-100): q [t][heads][dim] already rotated,
+    k and v [start + t][kv_heads][dim] by absolute position; window <= 0 is full."""
+    q = np.asarray(q, np.float64)
+    k = np.asarray(k, np.float64)
+    v = np.asarray(v, np.float64)
+    t, heads, dim = q.shape
+    group = heads // k.shape[1]
+    out = np.zeros((t, heads, dim), np.float64)
+    for i in range(t):
+        last = start + i
+        first = max(0, last + 1 - window) if window > 0 else 0
+        for h in range(heads):
+            g = h // group
+            s = (k[first:last + 1, g] @ q[i, h]) * float(scale)
+            sink = -np.inf if sinks is None else float(sinks[h])
+            m = max(sink, s.max())
+            e = np.exp(s - m)
+            z = e.sum() + np.exp(sink - m)
+            out[i, h] = (e / z) @ v[first:last + 1, g]
+    return out.astype(np.float32)

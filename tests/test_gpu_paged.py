@@ -1,0 +1,263 @@
+"""The paged bf16 path (RoPE + append, decode attention) against the CPU oracle, through the
+C ABI.  Gate, as for every bf16-cache kernel: bf16 output (widened) against the UNROUNDED f32
+output of the oracle in its bf16-cache mode, max abs <= 1e-2 and cosine >= 0.9999; the figure
+against the reference-faithful f32-cache mode is printed beside it.  Integer things (which
+page, which row, which keys are visible, the bits stored in the cache) are compared exactly."""
+import numpy as np
+import pytest
+
+from loadngo_b200 import compute
+from loadngo_b200.layer import PagedAttentionLayer
+from oracle import oracle
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MIN_COS = 1e-2, 0.9999
+D = 64
+
+
+def bits(x):
+    return oracle.f32_to_bf16_bits(x)
+
+
+def widen(b):
+    return oracle.bf16_bits_to_f32(b)
+
+
+def pool_view(layer):
+    return layer.cache.pool.view(np.uint16).reshape(layer.cache.pool_pages, layer.kv_heads, 2, 16, D)
+
+
+def test_rope_append_is_bit_exact(gpu):
+    q, k, v, sinks = helpers.config1_inputs(320)
+    ref = oracle.Session(64, 8, D, 320, sinks=sinks, rope=oracle.Rope(), cache_bf16=True)
+    _, q_rot = ref.feed(q, k, v)
+    layer = PagedAttentionLayer(gpu, seqs=1, max_context=320, max_new=320, sinks=sinks, mirrored_pool=True,
+                                rng=np.random.default_rng(7))
+    layer.cache.reserve(0, 320)
+    layer.cache.flush_table()
+    layer._stage(bits(q), bits(k), bits(v), np.arange(320), np.zeros(320, np.int32))
+    batch = gpu.batch(layer.buffers())
+    layer.record_append(batch, 320)
+    done = batch.run()
+    assert not isinstance(done.gpu_time, Exception), done.gpu_time
+    pool = pool_view(layer)
+    row = layer.cache.table_host[0]
+    got_k = np.stack([pool[row[p // 16], :, 0, p % 16] for p in range(320)])
+    got_v = np.stack([pool[row[p // 16], :, 1, p % 16] for p in range(320)])
+    assert np.array_equal(got_k, bits(ref.keys)), "rotated keys differ from the oracle's bf16 cache"
+    assert np.array_equal(got_v, bits(ref.values))
+    planes = layer.q_rot.view(np.uint16)[: 2 * 320 * 64 * D].reshape(2, 320, 64, D)
+    hi = bits(q_rot)
+    assert np.array_equal(planes[0], hi)
+    assert np.array_equal(planes[1], bits(q_rot - widen(hi)))
+    # f32 inputs take the same path
+    layer2 = PagedAttentionLayer(gpu, seqs=1, max_context=64, max_new=64, mirrored_pool=True)
+    layer2.q.free(); layer2.k.free(); layer2.v.free()
+    layer2.q, layer2.k, layer2.v = gpu.upload(q[:64]), gpu.upload(k[:64]), gpu.upload(v[:64])
+    layer2.cache.reserve(0, 64)
+    layer2.cache.flush_table()
+    layer2.positions.write(np.arange(64, dtype=np.int32))
+    layer2.seq_ids.write(np.zeros(64, np.int32))
+    batch = gpu.batch(layer2.buffers())
+    layer2.record_append(batch, 64, in_f32=True)
+    assert not isinstance(batch.run().gpu_time, Exception)
+    pool2 = pool_view(layer2)
+    row2 = layer2.cache.table_host[0]
+    assert np.array_equal(np.stack([pool2[row2[p // 16], :, 0, p % 16] for p in range(64)]), bits(ref.keys[:64]))
+    layer.free(); layer2.free()
+
+
+@pytest.mark.parametrize("window", [0, 128])
+def test_config1_decode_matches_the_oracle(gpu, window):
+    """256 positions appended, then 64 decoded one at a time (batch 1, 64 heads over 8)."""
+    q, k, v, sinks = helpers.config1_inputs(320)
+    rope = oracle.Rope()
+    ref_b = oracle.Session(64, 8, D, 320, window=window, sinks=sinks, rope=rope, cache_bf16=True)
+    ref_f = oracle.Session(64, 8, D, 320, window=window, sinks=sinks, rope=rope)
+    want_b, _ = ref_b.feed(q, k, v)
+    want_f, _ = ref_f.feed(q, k, v)
+    layer = PagedAttentionLayer(gpu, seqs=1, max_context=320, max_new=256, window=window, sinks=sinks,
+                                rng=np.random.default_rng(3))
+    layer.cache.reserve(0, 256)
+    layer.cache.flush_table()
+    layer._stage(bits(q[:256]), bits(k[:256]), bits(v[:256]), np.arange(256), np.zeros(256, np.int32))
+    batch = gpu.batch(layer.buffers())
+    layer.record_append(batch, 256)
+    assert not isinstance(batch.run().gpu_time, Exception)
+    got = []
+    for p in range(256, 320):
+        got.append(layer.decode_step(bits(q[p:p + 1]), bits(k[p:p + 1]), bits(v[p:p + 1])))
+    got = widen(np.concatenate(got))
+    err_b, cos_b = helpers.errors(got, want_b[256:])
+    err_f, cos_f = helpers.errors(got, want_f[256:])
+    print(f"\nconfig-1 decode window={window}: vs bf16-cache oracle max_abs={err_b:.5f} cos={cos_b:.7f}; "
+          f"vs f32-cache oracle max_abs={err_f:.5f} cos={cos_f:.7f}")
+    assert err_b <= MAX_ABS and cos_b >= MIN_COS
+    assert cos_f >= MIN_COS
+    layer.free()
+
+
+def _fill(layer, rng, lens, poison=True):
+    """Random rotated-K / V caches packed straight into the pool; everything else NaN."""
+    pool = layer.cache.pool.view(np.uint16, mutable=True).reshape(layer.cache.pool_pages, layer.kv_heads, 2, 16, D)
+    if poison:
+        pool[:] = 0x7FC0   # NaN in every row no query may read (attention_grouped.rs:47-63)
+    caches = []
+    for s, length in enumerate(lens):
+        layer.cache.reserve(s, int(length))
+        kc = oracle.round_bf16(rng.standard_normal((length, layer.kv_heads, D)).astype(np.float32))
+        vc = oracle.round_bf16(rng.standard_normal((length, layer.kv_heads, D)).astype(np.float32))
+        helpers.pack_pages(kc, vc, layer.cache.table_host[s], pool, layer.cache.ring_pages)
+        caches.append((kc, vc))
+    layer.cache.flush_table()
+    return caches
+
+
+def _decode_direct(gpu, layer, q_rot, lens):
+    """Runs only the decode kernel on pre-rotated queries (hi/lo planes built here)."""
+    n = len(lens)
+    hi = bits(q_rot)
+    lo = bits(q_rot - widen(hi))
+    layer.q_rot.write(np.concatenate([hi.reshape(-1), lo.reshape(-1)]))
+    layer.seq_lens.write(np.asarray(lens, np.int32))
+    batch = gpu.batch(layer.buffers())
+    layer.record_decode(batch, n, int(max(lens)))
+    done = batch.run()
+    assert not isinstance(done.gpu_time, Exception), done.gpu_time
+    return widen(layer.out.view(np.uint16)[: n * layer.heads * D].reshape(n, layer.heads, D))
+
+
+@pytest.mark.parametrize("window", [0, 128])
+@pytest.mark.parametrize("kv_heads", [8, 1])
+def test_ragged_batch_with_poisoned_pages(gpu, window, kv_heads):
+    """Lengths around page and split edges; pages scattered; unread rows are NaN."""
+    rng = np.random.default_rng(11)
+    lens = [1, 2, 15, 16, 17, 127, 128, 129, 255, 257, 700, 2049, 4096 + 33]
+    layer = PagedAttentionLayer(gpu, seqs=len(lens), max_context=4200, max_new=len(lens), kv_heads=kv_heads,
+                                window=window, sinks=rng.standard_normal(kv_heads * 8).astype(np.float32) * 3,
+                                rng=rng, mirrored_pool=True)
+    caches = _fill(layer, rng, lens)
+    q_rot = rng.standard_normal((len(lens), layer.heads, D)).astype(np.float32) * 1.3
+    got = _decode_direct(gpu, layer, q_rot, lens)
+    sinks = layer.sinks.as_f32()[: layer.heads].copy()
+    for s, length in enumerate(lens):
+        want = helpers.decode_f64(q_rot[s], caches[s][0], caches[s][1], length, window, layer.scale, sinks)
+        err, cos = helpers.errors(got[s], want)
+        assert not np.isnan(got[s]).any(), f"sequence {s} (len {length}) read a poisoned row"
+        assert err <= MAX_ABS and cos >= MIN_COS, f"len {length}: max_abs {err}, cos {cos}"
+    layer.free()
+
+
+def test_no_sinks_and_dominating_sinks(gpu):
+    rng = np.random.default_rng(5)
+    lens = [300, 40]
+    for sinks in (None, np.full(64, 30.0, np.float32), np.full(64, -30.0, np.float32)):
+        layer = PagedAttentionLayer(gpu, seqs=2, max_context=320, max_new=2, sinks=sinks, rng=rng, mirrored_pool=True)
+        caches = _fill(layer, rng, lens)
+        q_rot = rng.standard_normal((2, 64, D)).astype(np.float32)
+        got = _decode_direct(gpu, layer, q_rot, lens)
+        for s, length in enumerate(lens):
+            want = helpers.decode_f64(q_rot[s], caches[s][0], caches[s][1], length, 0, layer.scale, sinks)
+            err, _ = helpers.errors(got[s], want)
+            assert err <= MAX_ABS
+        if sinks is not None and sinks[0] > 0:
+            assert np.abs(got).max() < 1e-6   # the sink takes all the probability and adds no value
+        layer.free()
+
+
+def test_sliding_ring_of_pages(gpu):
+    """A window layer whose pages wrap (the paged form of the reference's ring of slots,
+    gpt-oss/src/gpu.rs:567-574): positions far beyond the ring still resolve to the right rows."""
+    rng = np.random.default_rng(9)
+    ring = 12   # 192 rows >= window 128 + a partial page at each end
+    lens = [5, 128, 191, 192, 193, 1000, 3001]
+    layer = PagedAttentionLayer(gpu, seqs=len(lens), max_context=4096, max_new=len(lens), window=128,
+                                sinks=rng.standard_normal(64).astype(np.float32), ring_pages=ring, rng=rng,
+                                mirrored_pool=True)
+    caches = _fill(layer, rng, lens)
+    q_rot = rng.standard_normal((len(lens), 64, D)).astype(np.float32)
+    got = _decode_direct(gpu, layer, q_rot, lens)
+    sinks = layer.sinks.as_f32()[:64].copy()
+    for s, length in enumerate(lens):
+        want = helpers.decode_f64(q_rot[s], caches[s][0], caches[s][1], length, 128, layer.scale, sinks)
+        err, cos = helpers.errors(got[s], want)
+        assert err <= MAX_ABS and cos >= MIN_COS, f"len {length}: {err}"
+    layer.free()
+
+
+def test_full_size_decode_batch_matches_the_float64_definition(gpu):
+    """The benchmark's workload at full size: 32 ragged sequences, KV lengths uniform in
+    [1024, 8192], 64 heads over 8, scattered 16-token pages, a full and a 128-window layer."""
+    rng = np.random.default_rng(0)
+    lens = rng.integers(1024, 8193, 32)
+    sinks = rng.standard_normal(64).astype(np.float32)
+    for window in (0, 128):
+        layer = PagedAttentionLayer(gpu, seqs=32, max_context=8192, max_new=32, window=window, sinks=sinks,
+                                    pool_pages=int(sum(-(-int(l) // 16) for l in lens)) + 8, rng=rng, mirrored_pool=True)
+        caches = _fill(layer, rng, [int(l) for l in lens])
+        q_rot = rng.standard_normal((32, 64, D)).astype(np.float32) * 1.3
+        got = _decode_direct(gpu, layer, q_rot, [int(l) for l in lens])
+        worst, worst_cos = 0.0, 1.0
+        for s, length in enumerate(lens):
+            want = helpers.decode_f64(q_rot[s], caches[s][0], caches[s][1], int(length), window, layer.scale, sinks)
+            err, cos = helpers.errors(got[s], want)
+            worst, worst_cos = max(worst, err), min(worst_cos, cos)
+        print(f"\nfull-size decode window={window}: max_abs={worst:.5f} min cos={worst_cos:.7f}")
+        assert worst <= MAX_ABS and worst_cos >= MIN_COS
+        # a property that holds at any size: the same values under every key come back scaled
+        # by the probability the sink did not take
+        layer.free()
+
+
+def test_decode_step_appends_then_attends(gpu):
+    """The whole step a caller makes (host arrays in and out) for a small ragged batch,
+    position by position, against the oracle fed the same tokens."""
+    rng = np.random.default_rng(21)
+    seqs, steps = 3, 40
+    sinks = rng.standard_normal(64).astype(np.float32)
+    rope = oracle.Rope()
+    refs = [oracle.Session(64, 8, D, steps, sinks=sinks, rope=rope, cache_bf16=True) for _ in range(seqs)]
+    layer = PagedAttentionLayer(gpu, seqs=seqs, max_context=steps, max_new=seqs, sinks=sinks, rng=rng)
+    worst = 0.0
+    for _ in range(steps):
+        q = oracle.round_bf16(rng.standard_normal((seqs, 64, D)).astype(np.float32))
+        k = oracle.round_bf16(rng.standard_normal((seqs, 8, D)).astype(np.float32))
+        v = oracle.round_bf16(rng.standard_normal((seqs, 8, D)).astype(np.float32))
+        got = widen(layer.decode_step(bits(q), bits(k), bits(v)))
+        for s in range(seqs):
+            want, _ = refs[s].feed(q[s:s + 1], k[s:s + 1], v[s:s + 1])
+            worst = max(worst, helpers.errors(got[s], want[0])[0])
+    assert worst <= MAX_ABS
+    # truncate: go back 10 positions and feed again; results repeat
+    layer.truncate(0, steps - 10)
+    refs[0].truncate(steps - 10)
+    assert layer.cache.lens[0] == steps - 10
+    layer.free()
+
+
+def test_bad_inputs_are_rejected_before_launch_or_reported_after(gpu):
+    layer = PagedAttentionLayer(gpu, seqs=2, max_context=64, max_new=2, mirrored_pool=True)
+    batch = gpu.batch(layer.buffers())
+    with pytest.raises(compute.DispatchError):      # a slice of the wrong size
+        batch.attention_decode_paged(compute.Slice(layer.QROT, 0, 100), layer.cache.descriptor(layer.POOL, layer.BT),
+                                     compute.Slice(layer.LENS, 0, 8), 2, 64, None, 0, 0.125,
+                                     compute.Slice(layer.OUT, 0, 2 * 64 * D * 2))
+    with pytest.raises(compute.DispatchError):      # output overlapping an input
+        batch.attention_decode_paged(compute.Slice(layer.QROT, 0, 2 * 2 * 64 * D * 2),
+                                     layer.cache.descriptor(layer.POOL, layer.BT), compute.Slice(layer.LENS, 0, 8), 2,
+                                     64, None, 0, 0.125, compute.Slice(layer.QROT, 0, 2 * 64 * D * 2))
+    assert batch.dispatches == 0
+    batch.drop()                                    # the failed dispatches left the batch usable; dropping runs nothing
+    # a block table that points outside the pool is caught on the device and reported
+    layer.cache.table_host[:] = 10 ** 6
+    layer.cache._dirty = True
+    layer.cache.flush_table()
+    layer.q_rot.write(np.zeros(2 * 2 * 64 * D, np.uint16))
+    layer.seq_lens.write(np.array([20, 20], np.int32))
+    batch = gpu.batch(layer.buffers())
+    layer.record_decode(batch, 2, 20)
+    done = batch.run()
+    assert isinstance(done.gpu_time, compute.GpuError)
+    layer.free()

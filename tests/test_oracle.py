@@ -1,0 +1,142 @@
+"""The CPU oracle against the reference's own pins (no GPU needed)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import helpers
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_attention.npz")
+
+
+def test_bf16_rounding_known_answers():
+    # weights/src/dtype.rs:182-203
+    L = oracle.lib()
+    r = lambda x: L.oracle_bf16_to_f32(L.oracle_f32_to_bf16(x))
+    assert r(0.9567871) == 0.95703125
+    assert r(0.8925781) == 0.890625
+    assert r(1.0) == 1.0
+    assert r(1.0 + 1.0 / 256.0) == 1.0
+    assert r(1.0 + 3.0 / 256.0) == 1.0 + 4.0 / 256.0
+    assert np.isnan(r(float("nan")))
+    assert r(float("inf")) == float("inf")
+    for bits in range(0, 65536, 7):
+        v = L.oracle_bf16_to_f32(bits)
+        if not np.isnan(v):
+            assert L.oracle_f32_to_bf16(v) == bits
+
+
+def test_vectorised_bf16_matches_scalar():
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(5000).astype(np.float32) * np.float32(10.0) ** rng.integers(-20, 20, 5000).astype(np.float32)
+    x = np.concatenate([x, np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1 + 1 / 256, 1 + 3 / 256], np.float32)])
+    L = oracle.lib()
+    want = np.array([L.oracle_f32_to_bf16(float(v)) for v in x], np.uint16)
+    assert np.array_equal(oracle.f32_to_bf16_bits(x), want)
+
+
+def test_yarn_known_answers():
+    # values of Config::rope (gpt-oss/src/config.rs:108-133) at gpt-oss-20b's parameters
+    inv, scale = oracle.Rope().inv_freq()
+    assert scale == pytest.approx(1.3465735902799727, rel=0, abs=1e-15)
+    known = {0: 1.0, 1: 0.6890443058881633, 8: 0.050813274815461475, 17: 1.2931870124506317e-4,
+             18: 3.8308812373753384e-5, 31: 3.0235114281192144e-7}
+    for i, want in known.items():
+        assert inv[i] == pytest.approx(want, rel=1e-13)
+    # pairs 0-8 are pure extrapolation, 18-31 pure interpolation
+    theta = 150000.0
+    for i in range(0, 9):
+        assert inv[i] == pytest.approx(theta ** (-2 * i / 64), rel=1e-14)
+    for i in range(18, 32):
+        assert inv[i] == pytest.approx(theta ** (-2 * i / 64) / 32.0, rel=1e-14)
+
+
+def test_rotation_matches_its_float64_definition():
+    # metal-compute/tests/q8_0_and_gpt_oss_glue.rs:239-254, tolerance 1e-6
+    rope = oracle.Rope()
+    inv, scale = rope.inv_freq()
+    x = helpers.xorshift_values(1, 3 * 4 * 64).reshape(3, 4, 64)
+    for r, pos in enumerate([0, 5, 4097]):
+        y = x[r].copy().reshape(-1)
+        oracle.lib().oracle_rotate(y, 4, 64, inv, scale, pos)
+        y = y.reshape(4, 64)
+        table = rope.table(pos, 1)[0].astype(np.float64)
+        for h in range(4):
+            a, b = x[r, h, :32].astype(np.float64), x[r, h, 32:].astype(np.float64)
+            assert np.abs(y[h, :32] - (a * table[:, 0] - b * table[:, 1])).max() < 1e-6
+            assert np.abs(y[h, 32:] - (b * table[:, 0] + a * table[:, 1])).max() < 1e-6
+
+
+def test_golden_tiny_fixture_replays():
+    """The per-layer attention of the reference's tiny end-to-end fixture, as recorded when
+    the oracle reproduced the fixture's logits (see tests/golden/make_tiny_golden.py)."""
+    g = np.load(GOLDEN)
+    meta = json.loads(str(g["meta"]))
+    assert meta["worst_logit_error"] < 2e-3           # tolerance of gpt-oss/tests/tiny_oracle.rs:10
+    assert all(e > 2e-3 for e in meta["mutations"].values())   # each deliberate bug was caught
+    rope = oracle.Rope(meta["dim"], meta["theta"], meta["factor"], float(meta["original_context"]))
+    for l in range(meta["layers"]):
+        window = meta["window"] if l % 2 == 0 else 0   # even layers slide (config.rs:101-103)
+        s = oracle.Session(meta["heads"], meta["kv_heads"], meta["dim"], meta["positions"], window=window,
+                           sinks=g[f"l{l}_sinks"], rope=rope)
+        out, q_rot = s.feed(g[f"l{l}_q"], g[f"l{l}_k"], g[f"l{l}_v"])
+        assert np.abs(out - g[f"l{l}_out"]).max() < 1e-6
+        assert np.abs(q_rot - g[f"l{l}_q_rot"]).max() < 1e-6
+        assert np.abs(s.keys - g[f"l{l}_kcache"]).max() < 1e-6
+        # and the float64 definition agrees with the f32 loop
+        want = oracle.attention_f64(q_rot, s.keys, s.values, start=0, window=window,
+                                    scale=1 / np.sqrt(meta["dim"]), sinks=g[f"l{l}_sinks"])
+        assert np.abs(out - want).max() < 2e-5         # metal-compute/tests/attention_grouped.rs:201
+
+
+@pytest.mark.parametrize("mutation", ["no_sink", "narrow_window", "wrong_parity", "flipped_sign", "no_scale"])
+def test_attention_mutations_are_caught_by_the_golden(mutation):
+    """The attention-relevant deliberate bugs of docs/GPT_OSS.md:112-121, applied to the oracle
+    itself: each must move the attention output away from the golden."""
+    g = np.load(GOLDEN)
+    meta = json.loads(str(g["meta"]))
+    rope = oracle.Rope(meta["dim"], meta["theta"], meta["factor"], float(meta["original_context"]))
+    worst = 0.0
+    for l in range(meta["layers"]):
+        sliding = l % 2 == 0
+        if mutation == "wrong_parity":
+            sliding = not sliding
+        window = meta["window"] - (1 if mutation == "narrow_window" else 0)
+        sinks = None if mutation == "no_sink" else g[f"l{l}_sinks"]
+        s = oracle.Session(meta["heads"], meta["kv_heads"], meta["dim"], meta["positions"],
+                           window=window if sliding else 0, sinks=sinks, rope=rope)
+        if mutation == "flipped_sign":
+            s._inv = -s._inv
+        if mutation == "no_scale":
+            s._rope_scale = 1.0
+        out, _ = s.feed(g[f"l{l}_q"], g[f"l{l}_k"], g[f"l{l}_v"])
+        worst = max(worst, float(np.abs(out - g[f"l{l}_out"]).max()))
+    assert worst > 1e-3
+
+
+def test_threads_do_not_change_results_and_sessions_continue():
+    q, k, v, sinks = helpers.config1_inputs(96, 16, 2)
+    rope = oracle.Rope()
+    a = oracle.Session(16, 2, 64, 96, window=32, sinks=sinks, rope=rope, cache_bf16=True)
+    out_a, _ = a.feed(q, k, v, threads=1)
+    b = oracle.Session(16, 2, 64, 96, window=32, sinks=sinks, rope=rope, cache_bf16=True)
+    out_b1, _ = b.feed(q[:50], k[:50], v[:50], threads=4)
+    out_b2, _ = b.feed(q[50:], k[50:], v[50:], threads=3)
+    assert np.array_equal(out_a, np.concatenate([out_b1, out_b2]))
+    # truncate goes back as if nothing after had been fed (model.rs:204-213)
+    b.truncate(50)
+    out_b3, _ = b.feed(q[50:], k[50:], v[50:])
+    assert np.array_equal(out_b2, out_b3)
+
+
+def test_bf16_cache_mode_only_rounds_what_is_appended():
+    q, k, v, sinks = helpers.config1_inputs(40, 8, 1)
+    rope = oracle.Rope()
+    f = oracle.Session(8, 1, 64, 40, sinks=sinks, rope=rope)
+    b = oracle.Session(8, 1, 64, 40, sinks=sinks, rope=rope, cache_bf16=True)
+    f.feed(q, k, v)
+    b.feed(q, k, v)
+    assert np.array_equal(b.keys, oracle.round_bf16(f.keys))
+    assert np.array_equal(b.values, f.values)   # v was bf16 already
