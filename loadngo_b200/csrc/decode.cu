@@ -158,9 +158,20 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_consta
         x[3] = (s1[1] + s1[3]) * p.scale_log2e;
         if (lp == page_lo || lp == page_hi) {  // only edge pages hold keys outside [first, L)
             const int kp[4] = {key0, key0 + 1, key0 + 8, key0 + 9};
+            uint32_t keep[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (kp[e] < first || kp[e] >= L) x[e] = neg_inf();
+            for (int e = 0; e < 4; ++e) {
+                const bool visible = kp[e] >= first && kp[e] < L;
+                if (!visible) x[e] = neg_inf();
+                keep[e] = visible ? 0xffffu : 0u;
+            }
+            // Rows outside the visible range may hold anything (NaN included): their weight is
+            // zero, and their values are zeroed too so that 0 * NaN cannot reach the output.
+            const uint32_t m01 = keep[0] | (keep[1] << 16), m23 = keep[2] | (keep[3] << 16);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                vb[c][0] &= m01; vb[c][1] &= m23; vb[c][2] &= m01; vb[c][3] &= m23;
+            }
         }
         float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
