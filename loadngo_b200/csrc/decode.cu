@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_consta
         if (p.ring_pages) idx %= p.ring_pages;
         int32_t page = idx < p.max_pages ? table_row[idx] : -1;
         if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages) {
-            atomicMax(p.status, kStatusBadPage);
+            raise_status(p.status, kStatusBadPage);
             page = 0;  // still complete the copy so the pipeline drains; the status marks the result invalid
         }
         const int stage = it % kStages;
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_consta
             mma_bf16_16816(o[2 * c + 1], ph0, pl0, ph1, pl1, vb[c][2], vb[c][3]);
         }
     }
-    if (failed && lane == 0) atomicMax(p.status, kStatusWaitTimeout);
+    if (failed && lane == 0) raise_status(p.status, kStatusWaitTimeout);
 
     // ---- merge the 4 warps (each warp's own, now idle, tile region is its mailbox) ---------
     l += __shfl_xor_sync(0xffffffffu, l, 1);

@@ -94,6 +94,12 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Raises the device status word to `code` (kept at the largest code seen); a null word means
+// the caller did not ask for device-side reports.
+__device__ __forceinline__ void raise_status(uint32_t *status, uint32_t code) {
+    if (status) atomicMax(status, code);
+}
+
 // ---- bfloat16 ------------------------------------------------------------------------------
 // Round to nearest, ties to even, on the bit pattern; a NaN keeps its top payload bits and
 // is made quiet.  Matches loadngo's weights/src/dtype.rs:102-110 bit for bit.

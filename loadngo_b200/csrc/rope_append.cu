@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         const int64_t pos = p.positions[token];
         const int64_t row = pos - p.table_start;
         if (pos < 0 || row < 0 || row >= p.table_rows) {
-            atomicMax(p.status, kStatusBadTableRow);
+            raise_status(p.status, kStatusBadTableRow);
             continue;
         }
         const float *cs_row = p.table + row * (kHeadDim / 2) * 2;
@@ -101,12 +101,12 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         uint32_t logical = static_cast<uint32_t>(pos / kPageTokens);
         if (p.ring_pages) logical %= p.ring_pages;
         if (logical >= p.max_pages) {
-            atomicMax(p.status, kStatusBadPage);
+            raise_status(p.status, kStatusBadPage);
             continue;
         }
         const int32_t page = p.block_table[static_cast<size_t>(seq) * p.max_pages + logical];
         if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages) {
-            atomicMax(p.status, kStatusBadPage);
+            raise_status(p.status, kStatusBadPage);
             continue;
         }
         const uint32_t slot = static_cast<uint32_t>(pos % kPageTokens);
