@@ -139,6 +139,24 @@ int cc_attention_decode_paged(void *stream, const cc_decode_args *args);
 size_t cc_decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_seq_len, uint32_t window,
                                  uint32_t pages_per_split);
 
+/* The same decode attention for callers that must not allocate device memory.  It has no
+ * counterpart in loadngo: metal-compute allocates freely from unified memory.  Who needs it: a
+ * host that gave all of HBM to its page pool and weights at start-up (a later cudaMalloc would
+ * fail), and a model thread that may never stall between submissions (cudaMalloc and cudaFree
+ * synchronise the device).  The scratch is a fixed CC_DECODE_STATIC_SCRATCH_BYTES array inside the
+ * library image, held by every GPU that loads the library until the process exits; `workspace`
+ * and `workspace_bytes` of `args` are ignored.  Returns CC_ALLOC, launching nothing, when
+ * cc_decode_workspace_bytes() for these sizes exceeds the array (give a larger
+ * pages_per_split, or use cc_attention_decode_paged).  The first call on each device looks the
+ * array's device address up; make that first call outside any stream capture.  All calls on a
+ * device share the one array: calls whose kernels could overlap on the GPU (different streams)
+ * race; calls on one stream are safe, each clears the counters it depends on first.  Calls no
+ * cudaMalloc, cudaFree or other allocating routine; last-error text is that of
+ * cc_attention_decode_paged when the failure comes from it. */
+#define CC_DECODE_STATIC_SCRATCH_BYTES (16u << 20)
+int cc_attention_decode_paged_static(void *stream, const cc_decode_args *args);
+size_t cc_decode_static_scratch_bytes(void);
+
 /* Prefill attention: t_b new positions per sequence against the cache (which already holds
  * them: call cc_rope_append_paged first).  Replaces Batch::attention_grouped_tiled_with_sinks
  * (metal-compute/src/apple.rs:1324-1401, kernel `attention_grouped_tiled`

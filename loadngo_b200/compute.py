@@ -131,6 +131,8 @@ SYMBOLS = {
     "cc_attention_decode_paged": (c_int, [c_void_p, POINTER(DecodeArgs)]),
     "cc_decode_workspace_bytes": (c_size_t, [c_uint32, c_uint32, c_uint32, c_uint32, c_uint32]),
     "cc_attention_prefill_paged": (c_int, [c_void_p, POINTER(PrefillArgs)]),
+    "cc_attention_decode_paged_static": (c_int, [c_void_p, POINTER(DecodeArgs)]),
+    "cc_decode_static_scratch_bytes": (c_size_t, []),
     "cc_gpu_new": (c_int, [c_int, POINTER(c_void_p)]),
     "cc_gpu_free": (None, [c_void_p]),
     "cc_gpu_stream": (c_void_p, [c_void_p]),

@@ -108,6 +108,11 @@ uint32_t choose_pages_per_split(uint32_t seqs, uint32_t kv_heads, uint32_t pages
 
 }  // namespace
 
+// Lets the library's other source files leave a message for cc_last_error().
+namespace cc {
+int set_error(int code, const char *text) { return fail(static_cast<cc_status>(code), "%s", text); }
+}  // namespace cc
+
 // =================================================================================================
 // A. status
 // =================================================================================================

@@ -55,6 +55,9 @@ void launch_decode(const DecodeParams &p, cudaStream_t stream);
 // Bytes of scratch `launch_decode` needs for the given sizes (partials + counters).
 size_t decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_splits);
 
+// Records `text` as the calling thread's last error (what cc_last_error returns); returns `code`.
+int set_error(int code, const char *text);
+
 // Error codes kernels write to the status word.
 enum : uint32_t {
     kStatusOk = 0,

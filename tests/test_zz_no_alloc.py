@@ -1,0 +1,102 @@
+"""cc_attention_decode_paged_static: decode attention whose scratch is a fixed array inside the
+library, for callers that cannot allocate device memory (a host whose HBM is fully committed to
+its page pool, or a model thread that may not stall on cudaMalloc's device-wide synchronisation).
+
+Collected last on purpose.  It drives the new entry point through the C ABI and checks that it
+gives what the existing entry point gives with a caller-owned workspace, twice in a row with
+different shapes, so that what the first call left in the shared array cannot leak into the
+second.  It must pass on its own and after every other test."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from loadngo_b200 import compute
+from loadngo_b200.layer import PagedAttentionLayer
+from oracle import oracle
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+D = 64
+
+
+def _args(layer, n, lens, workspace=None, workspace_bytes=0):
+    heads = layer.heads
+    q = layer.q_rot.device_ptr
+    return compute.DecodeArgs(
+        q, q + n * heads * D * 2, layer.cache.pool.device_ptr, layer.cache.pool_pages,
+        layer.cache.table.device_ptr, layer.cache.max_pages, 0, layer.seq_lens.device_ptr, n, int(max(lens)),
+        layer.sinks.device_ptr, heads, layer.kv_heads, layer.window, layer.scale, layer.out.device_ptr,
+        workspace, workspace_bytes, 0, None)
+
+
+def _run_case(gpu, rng, lens, window):
+    L = compute.lib()
+    n = len(lens)
+    layer = PagedAttentionLayer(gpu, seqs=n, max_context=int(max(lens)) + 16, max_new=n, window=window,
+                                sinks=rng.standard_normal(64).astype(np.float32), rng=rng, mirrored_pool=True)
+    pool = layer.cache.pool.view(np.uint16, mutable=True).reshape(layer.cache.pool_pages, 8, 2, 16, D)
+    caches = []
+    for s, length in enumerate(lens):
+        layer.cache.reserve(s, int(length))
+        kc = oracle.round_bf16(rng.standard_normal((length, 8, D)).astype(np.float32))
+        vc = oracle.round_bf16(rng.standard_normal((length, 8, D)).astype(np.float32))
+        helpers.pack_pages(kc, vc, layer.cache.table_host[s], pool)
+        caches.append((kc, vc))
+    layer.cache.flush_table()
+    q_rot = rng.standard_normal((n, 64, D)).astype(np.float32)
+    hi = oracle.f32_to_bf16_bits(q_rot)
+    lo = oracle.f32_to_bf16_bits(q_rot - oracle.bf16_bits_to_f32(hi))
+    layer.q_rot.write(np.concatenate([hi.reshape(-1), lo.reshape(-1)]))
+    layer.seq_lens.write(np.asarray(lens, np.int32))
+    # an empty batch uploads everything the host staged
+    batch = gpu.batch(layer.buffers())
+    assert not isinstance(batch.run().gpu_time, Exception)
+
+    def read_out():
+        gpu.synchronize()
+        # raw entries write device memory behind the buffer's back: copy it out through a batch
+        b = gpu.batch([layer.out, scratch_out])
+        b.copy_rows((compute.Slice(0, 0, n * 64 * D * 2), n * 64 * D // 2),
+                    (compute.Slice(1, 0, n * 64 * D * 2), n * 64 * D // 2), 1, n * 64 * D // 2)
+        assert not isinstance(b.run().gpu_time, Exception)
+        return oracle.bf16_bits_to_f32(scratch_out.view(np.uint16)[: n * 64 * D].copy()).reshape(n, 64, D)
+
+    scratch_out = gpu.buffer(n * 64 * D * 2)
+    # the existing entry point with a workspace of the caller's
+    need = L.cc_decode_workspace_bytes(n, 8, int(max(lens)), window, 0)
+    ws = gpu.device_buffer(need)
+    ws.zero()
+    a = _args(layer, n, lens, ws.device_ptr, need)
+    compute.check(L.cc_attention_decode_paged(gpu.stream, ctypes.byref(a)))
+    want = read_out()
+    # the new one: no workspace given
+    b = _args(layer, n, lens)
+    compute.check(L.cc_attention_decode_paged_static(gpu.stream, ctypes.byref(b)))
+    got = read_out()
+    err, cos = helpers.errors(got, want)
+    assert err <= 1e-2 and cos >= 0.9999, f"static-scratch decode differs from the workspace one: {err}"
+    # and both agree with the float64 definition
+    sinks = layer.sinks.as_f32()[:64].copy()
+    for s, length in enumerate(lens):
+        ref = helpers.decode_f64(q_rot[s], caches[s][0], caches[s][1], int(length), window, layer.scale, sinks)
+        assert helpers.errors(got[s], ref)[0] <= 1e-2
+    ws.free(); scratch_out.free(); layer.free()
+
+
+def test_static_scratch_decode_matches_the_workspace_entry_twice_in_a_row(gpu):
+    rng = np.random.default_rng(31)
+    assert compute.lib().cc_decode_static_scratch_bytes() == 16 << 20
+    _run_case(gpu, rng, [4097, 2500, 700, 33], 0)          # several splits per sequence
+    _run_case(gpu, rng, [900, 5000, 17, 1, 3100, 2049, 64], 0)   # other shape: stale scratch must not matter
+    _run_case(gpu, rng, [300, 129], 128)
+
+
+def test_static_scratch_rejects_what_does_not_fit(gpu):
+    L = compute.lib()
+    args = compute.DecodeArgs()
+    args.seqs, args.kv_heads, args.heads, args.max_seq_len, args.pages_per_split = 4096, 8, 64, 131072, 16
+    assert L.cc_decode_workspace_bytes(4096, 8, 131072, 0, 16) > L.cc_decode_static_scratch_bytes()
+    code = L.cc_attention_decode_paged_static(gpu.stream, ctypes.byref(args))
+    assert code == compute.Alloc.code
+    assert b"built-in array" in L.cc_last_error()
