@@ -333,6 +333,67 @@ class DecodeBench:
         return h2d, d2h
 
 
+class PrefillBench:
+    """BASELINE config 3: 4 sequences x 4096 new positions from an empty cache, one full-causal
+    and one 128-window layer; reported beside the decode headline."""
+    SEQS, T = 4, 4096
+
+    def __init__(self, gpu, kv_heads):
+        from loadngo_b200.layer import PagedAttentionLayer
+        from oracle import oracle  # bf16 rounding of the synthetic inputs only
+        rng = np.random.default_rng(3)
+        self.gpu, self.kv_heads, self.heads = gpu, kv_heads, kv_heads * GROUP
+        n = self.SEQS * self.T
+        bf = lambda shape: oracle.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32))
+        q, k, v = bf((n, self.heads, D)), bf((n, kv_heads, D)), bf((n, kv_heads, D))
+        self.layers = []
+        for window in (0, WINDOW):
+            layer = PagedAttentionLayer(gpu, seqs=self.SEQS, max_context=self.T, max_new=n, kv_heads=kv_heads,
+                                        window=window, sinks=rng.standard_normal(self.heads).astype(np.float32),
+                                        rng=rng)
+            for s in range(self.SEQS):
+                layer.cache.reserve(s, self.T)
+            layer.cache.flush_table()
+            layer._stage(q, k, v, np.tile(np.arange(self.T), self.SEQS), np.repeat(np.arange(self.SEQS), self.T))
+            layer.q_offsets.write((np.arange(self.SEQS + 1) * self.T).astype(np.int32))
+            layer.starts.write(np.zeros(self.SEQS, np.int32))
+            batch = gpu.batch(layer.buffers())
+            layer.record_append(batch, n)
+            done = batch.run()
+            if isinstance(done.gpu_time, Exception):
+                raise done.gpu_time
+            self.append_s = done.gpu_time
+            self.layers.append(layer)
+
+    def flops(self, window):
+        t = self.T
+        pairs = t * (t + 1) // 2 if not window else window * (window + 1) // 2 + (t - window) * window
+        return 4 * D * self.heads * pairs * self.SEQS
+
+    def run(self, layer_index, reps):
+        layer = self.layers[layer_index]
+        n = self.SEQS * self.T
+        batch = self.gpu.batch(layer.buffers())
+        for _ in range(reps):
+            layer.record_prefill(batch, self.SEQS, n, self.T)
+        done = batch.run()
+        if isinstance(done.gpu_time, Exception):
+            raise done.gpu_time
+        return done.gpu_time / reps
+
+    def free(self):
+        for layer in self.layers:
+            layer.free()
+
+
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["bf16_tflops"]), "measured (MEASURED_PEAKS.json, cuBLAS bf16 burst)"
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -399,6 +460,20 @@ def run_gpu(args):
     e2e_value = total_bytes * args.steps / e2e_s / 1e9
     h2d, d2h = bench.e2e_bytes()
 
+    # ---- prefill (config 3), reported beside the headline --------------------------------------
+    prefill = None
+    if not args.no_prefill:
+        pb = PrefillBench(gpu, len(heads_here))
+        tpeak, tpeak_kind = measured_tensor_peak()
+        prefill = {"workload": "4 x 4096 new positions from an empty cache, 64q/8kv/hd64 (per GPU: its KV heads)",
+                   "peak_tflops": tpeak, "peak_source": tpeak_kind, "rope_append_ms": pb.append_s * 1e3}
+        for li, name in ((0, "full_causal"), (1, "window_128")):
+            pb.run(li, 3)
+            sec = pb.run(li, 10)
+            tf = pb.flops(WINDOW if li else 0) / sec / 1e12
+            prefill[name] = {"ms": sec * 1e3, "tflops": tf, "frac_of_peak": tf / tpeak}
+        pb.free()
+
     if rank == 0:
         clock = clocks.summary()
         line = {
@@ -416,6 +491,8 @@ def run_gpu(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": full_bytes,
                          "us_per_launch": k_s / reps * 1e6},
         }
+        if prefill is not None:
+            line["prefill"] = prefill
         if world == 1 and not args.no_cpu:
             from oracle import oracle
             cores = 1
@@ -439,6 +516,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (config 3) section")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU baseline work")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -172,6 +172,7 @@ typedef struct cc_prefill_args {
     const int32_t *q_offsets;   /* [seqs + 1] first token row of each sequence in q/out */
     const int32_t *starts;      /* [seqs] absolute position of each sequence's first new token */
     uint32_t seqs;
+    uint32_t total_tokens;      /* rows of q and out (= q_offsets[seqs]) */
     uint32_t max_t;             /* host-side upper bound of the new positions per sequence */
     const float *sinks;
     uint32_t heads;

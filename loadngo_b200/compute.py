@@ -109,7 +109,7 @@ class PrefillArgs(Structure):
     _fields_ = [("q_hi", c_void_p), ("q_lo", c_void_p), ("pool", c_void_p), ("pool_pages", c_uint32),
                 ("block_table", c_void_p), ("max_pages", c_uint32), ("ring_pages", c_uint32),
                 ("q_offsets", c_void_p), ("starts", c_void_p), ("seqs", c_uint32),
-                ("max_t", c_uint32), ("sinks", c_void_p), ("heads", c_uint32),
+                ("total_tokens", c_uint32), ("max_t", c_uint32), ("sinks", c_void_p), ("heads", c_uint32),
                 ("kv_heads", c_uint32), ("window", c_uint32), ("scale", c_float),
                 ("out", c_void_p), ("status", c_void_p)]
 

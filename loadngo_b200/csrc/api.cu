@@ -84,6 +84,23 @@ int make_pool_map(CUtensorMap *map, const void *pool, uint64_t pool_pages, uint3
     return CC_OK;
 }
 
+// One bf16 plane of rotated queries [tokens][heads][64] as a 3-D tensor; a box is 128 token
+// rows of one head.
+int make_q_map(CUtensorMap *map, const void *q, uint64_t tokens, uint32_t heads) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return fail(CC_COMPILE, "cuTensorMapEncodeTiled is not available from this driver");
+    if (reinterpret_cast<uintptr_t>(q) % 16 != 0) return fail(CC_DISPATCH, "q: address is not 16-byte aligned");
+    cuuint64_t dims[3] = {cc::kHeadDim, heads, tokens};
+    cuuint64_t strides[2] = {cc::kHeadDim * 2, static_cast<cuuint64_t>(heads) * cc::kHeadDim * 2};
+    cuuint32_t box[3] = {cc::kHeadDim, 1, 128};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(q), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CC_DISPATCH, "q: tensor map rejected (CUresult %d)", static_cast<int>(r));
+    return CC_OK;
+}
+
 uint32_t div_up(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 
 // Pages a sequence of `max_seq_len` keys can show one query, and the split policy: enough
@@ -300,8 +317,53 @@ extern "C" int cc_attention_decode_paged(void *stream, const cc_decode_args *a) 
 }
 
 
-extern "C" int cc_attention_prefill_paged(void *, const cc_prefill_args *) {
-    return fail(CC_DISPATCH, "prefill: not built into this library yet");
+namespace {
+int prefill_prepare(const cc_prefill_args *a, uint32_t total_tokens, cc::PrefillParams *out) {
+    if (!a) return fail(CC_DISPATCH, "prefill: null arguments");
+    if (int rc = check_heads("prefill", a->heads, a->kv_heads)) return rc;
+    if (a->seqs == 0 || a->seqs > 65535) return fail(CC_DISPATCH, "prefill: %u sequences (1..65535)", a->seqs);
+    if (a->max_t == 0 || total_tokens == 0) return fail(CC_DISPATCH, "prefill: nothing to do");
+    if (!a->q_hi || !a->q_lo || !a->pool || !a->block_table || !a->q_offsets || !a->starts || !a->out)
+        return fail(CC_DISPATCH, "prefill: null pointer (both query planes are required)");
+    if (a->max_pages == 0 || a->pool_pages == 0) return fail(CC_DISPATCH, "prefill: empty block table or pool");
+    if (a->ring_pages > a->max_pages) return fail(CC_DISPATCH, "prefill: ring of %u pages in a table of %u",
+                                                  a->ring_pages, a->max_pages);
+    if (a->ring_pages != 0) {
+        if (a->window == 0) return fail(CC_DISPATCH, "prefill: a ring of pages needs a window");
+        // the ring must hold the window of the first new position through the last new position
+        const uint32_t need = div_up(a->window + a->max_t + cc::kPageTokens - 1, cc::kPageTokens);
+        if (a->ring_pages < need)
+            return fail(CC_DISPATCH, "prefill: a ring of %u pages cannot hold window %u plus %u new positions (%u pages)",
+                        a->ring_pages, a->window, a->max_t, need);
+    }
+    if (div_up(a->max_t, 128) > 65535) return fail(CC_DISPATCH, "prefill: %u new positions per sequence", a->max_t);
+    if (reinterpret_cast<uintptr_t>(a->out) % 16 != 0) return fail(CC_DISPATCH, "prefill: out is not 16-byte aligned");
+    cc::PrefillParams p{};
+    if (int rc = make_q_map(&p.q_hi_map, a->q_hi, total_tokens, a->heads)) return rc;
+    if (int rc = make_q_map(&p.q_lo_map, a->q_lo, total_tokens, a->heads)) return rc;
+    if (int rc = make_pool_map(&p.pool_map, a->pool, a->pool_pages, a->kv_heads, cc::kPageTokens)) return rc;
+    p.block_table = a->block_table;
+    p.q_offsets = a->q_offsets;
+    p.starts = a->starts;
+    p.sinks = a->sinks;
+    p.out = static_cast<uint16_t *>(a->out);
+    p.status = a->status;
+    p.seqs = a->seqs; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.max_pages = a->max_pages; p.ring_pages = a->ring_pages; p.pool_pages = a->pool_pages;
+    p.pool_rows = a->pool_pages * a->kv_heads * cc::kTileRows;
+    p.window = a->window;
+    p.max_t = a->max_t;
+    p.scale_log2e = a->scale * 1.4426950408889634f;
+    *out = p;
+    return CC_OK;
+}
+}  // namespace
+
+extern "C" int cc_attention_prefill_paged(void *stream, const cc_prefill_args *a) {
+    cc::PrefillParams p;
+    if (int rc = prefill_prepare(a, a ? a->total_tokens : 0, &p)) return rc;
+    cc::launch_prefill(p, static_cast<cudaStream_t>(stream));
+    return launch_status("prefill launch");
 }
 
 // =================================================================================================
@@ -958,10 +1020,47 @@ extern "C" int cc_batch_attention_decode_paged(cc_batch *b, cc_slice q_rot, cons
     return CC_OK;
 }
 
-extern "C" int cc_batch_attention_prefill_paged(cc_batch *, cc_slice, const cc_paged_cache *, cc_slice, cc_slice,
-                                                uint32_t, uint32_t, uint32_t, const cc_slice *, uint32_t, float,
-                                                cc_slice) {
-    return fail(CC_DISPATCH, "prefill: not built into this library yet");
+extern "C" int cc_batch_attention_prefill_paged(cc_batch *b, cc_slice q_rot, const cc_paged_cache *cache,
+                                                cc_slice q_offsets, cc_slice starts, uint32_t seqs,
+                                                uint32_t total_tokens, uint32_t max_t, const cc_slice *sinks,
+                                                uint32_t window, float scale, cc_slice out) {
+    if (!b) return fail(CC_DISPATCH, "prefill: null batch");
+    if (seqs == 0 || total_tokens == 0) return fail(CC_DISPATCH, "prefill: nothing to do");
+    uint8_t *pool, *bt;
+    uint32_t pool_pages, rows;
+    if (int rc = check_cache(b, cache, seqs, &pool, &pool_pages, &bt, &rows)) return rc;
+    const uint64_t heads = static_cast<uint64_t>(cache->kv_heads) * cc::kGroup;
+    uint8_t *pr, *pq, *pst, *po, *ps = nullptr;
+    if (int rc = check(b, "q_rot", q_rot, 2 * total_tokens * heads * 64 * 2, 16, &pr)) return rc;
+    if (int rc = check(b, "q_offsets", q_offsets, (static_cast<uint64_t>(seqs) + 1) * 4, 4, &pq)) return rc;
+    if (int rc = check(b, "starts", starts, static_cast<uint64_t>(seqs) * 4, 4, &pst)) return rc;
+    if (int rc = check(b, "out", out, total_tokens * heads * 64 * 2, 16, &po)) return rc;
+    if (int rc = check_output(b, out, {&q_rot, &cache->pool, &cache->block_table, &q_offsets, &starts, sinks})) return rc;
+    if (sinks)
+        if (int rc = check(b, "sinks", *sinks, heads * 4, 4, &ps)) return rc;
+    cc_prefill_args a{};
+    a.q_hi = pr;
+    a.q_lo = pr + total_tokens * heads * 64 * 2;
+    a.pool = pool; a.pool_pages = pool_pages;
+    a.block_table = reinterpret_cast<const int32_t *>(bt);
+    a.max_pages = cache->max_pages; a.ring_pages = cache->ring_pages;
+    a.q_offsets = reinterpret_cast<const int32_t *>(pq);
+    a.starts = reinterpret_cast<const int32_t *>(pst);
+    a.seqs = seqs; a.total_tokens = total_tokens; a.max_t = max_t;
+    a.sinks = reinterpret_cast<const float *>(ps);
+    a.heads = static_cast<uint32_t>(heads); a.kv_heads = cache->kv_heads;
+    a.window = window; a.scale = scale;
+    a.out = po;
+    a.status = b->gpu->status_dev;
+    cc::PrefillParams p;
+    if (int rc = prefill_prepare(&a, total_tokens, &p)) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_prefill(p, s);
+        return launch_status("prefill launch");
+    });
+    wrote(b, out);
+    ++b->dispatches;
+    return CC_OK;
 }
 
 extern "C" int cc_batch_read_back(cc_batch *b, cc_slice s) {

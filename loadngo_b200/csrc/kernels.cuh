@@ -55,6 +55,21 @@ void launch_decode(const DecodeParams &p, cudaStream_t stream);
 // Bytes of scratch `launch_decode` needs for the given sizes (partials + counters).
 size_t decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_splits);
 
+struct PrefillParams {
+    CUtensorMap q_hi_map, q_lo_map;  // [tokens][heads][64] bf16 as 3-D, box 64 x 1 x 128, 128B swizzle
+    CUtensorMap pool_map;            // rows of 64 bf16, box 64 x 16 (one page of K or of V)
+    const int32_t *block_table;      // [seqs][max_pages]
+    const int32_t *q_offsets;        // [seqs + 1]
+    const int32_t *starts;           // [seqs]
+    const float *sinks;              // [heads] or null
+    uint16_t *out;                   // [tokens][heads][64] bf16
+    uint32_t *status;
+    uint32_t seqs, heads, kv_heads, max_pages, ring_pages, pool_pages, pool_rows;
+    uint32_t window, max_t;
+    float scale_log2e;
+};
+void launch_prefill(const PrefillParams &p, cudaStream_t stream);
+
 // Records `text` as the calling thread's last error (what cc_last_error returns); returns `code`.
 int set_error(int code, const char *text);
 

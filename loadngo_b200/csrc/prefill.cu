@@ -1,0 +1,337 @@
+// Prefill (prompt-pass) attention for gpt-oss on sm_100a: tcgen05 tensor cores with TMEM
+// accumulators, operands staged by TMA, causal and sliding-window tile skipping.
+//
+// Replaces loadngo's `attention_grouped_tiled` (metal-compute/src/kernels.metal:588-720, host
+// entry metal-compute/src/apple.rs:1311-1401): for t new positions of a sequence starting at
+// `start`, every query attends the cache rows its causal / window rule allows
+// (gpt-oss/src/model.rs:434-438), with the head's sink logit in the softmax maximum and
+// denominator only (model.rs:449-455).  The new positions' keys and values are already in
+// the paged cache (the fused RoPE + append kernel ran first).
+//
+// One CTA = 128 queries of one head.  Six warps, three roles:
+//   warp 0  producer: TMA loads of the Q tile (hi and lo planes) and, per 128-key tile, eight
+//           16-key pages of K and of V, found through the block table, into 3-stage rings;
+//   warp 1  one thread issues tcgen05.mma: S = Qhi K^T + Qlo K^T (M128 N128 K64 twice) into one of
+//           two S buffers in TMEM, and O += P V (M128 N64 K128) into the O accumulator in TMEM;
+//   warps 2-5  softmax: one thread per query row reads its S row from TMEM, masks edge tiles,
+//           keeps the running maximum and sum, writes P as fp16 (11 significant bits; the
+//           weights lie in [0, 2^8]) into shared memory in the swizzled K-major layout the P V
+//           product reads (tcgen05 kind::f16 multiplies an fp16 A by a bf16 B), and rescales its O row in TMEM when
+//           its maximum moved by more than 2^8; at the end it folds the sink in, normalises and
+//           stores 128 bytes of bf16 output.
+// S is double-buffered so that S(j+1) = Q K(j+1)^T is computed while the softmax of tile j runs.
+// Tiles entirely outside a query tile's causal / window range are never visited (the loop
+// bounds exclude them, as kernels.metal:631-634 does); only edge tiles are masked per element.
+//
+// Every mbarrier wait is bounded; a wait that runs out raises the status word and the CTA
+// drains, frees its TMEM and returns.
+#include "kernels.cuh"
+#include "ptx.cuh"
+#include "tcgen05.cuh"
+
+namespace cc {
+namespace {
+
+constexpr int kTileQ = 128, kTileK = 128;
+constexpr int kStagesKV = 3;
+constexpr int kThreadsPrefill = 192;
+constexpr int kPlaneBytes = kTileQ * kHeadDim * 2;          // 16 KiB: 128 rows of 128 bytes
+constexpr int kOffQhi = 0;
+constexpr int kOffQlo = kPlaneBytes;
+constexpr int kOffK = 2 * kPlaneBytes;
+constexpr int kOffV = kOffK + kStagesKV * kPlaneBytes;
+constexpr int kOffP = kOffV + kStagesKV * kPlaneBytes;      // 2 buffers of 128 x 128 bf16
+constexpr int kOffBars = kOffP + 2 * 2 * kPlaneBytes;
+constexpr int kPrefillSmem = kOffBars + 256 + 1024;
+constexpr uint32_t kTmemCols = 512;                         // S0 0-127, S1 128-255, O 256-319
+constexpr uint32_t kColO = 256;
+constexpr float kRescaleThreshold = 8.0f;                   // log2 domain
+
+struct Bars {
+    uint64_t q_full;
+    uint64_t k_full[kStagesKV], k_empty[kStagesKV], v_full[kStagesKV], v_empty[kStagesKV];
+    uint64_t s_full[2], p_full[2], pv_done[2];
+    uint32_t tmem_base;
+    uint32_t pad;
+};
+
+__device__ __forceinline__ float neg_inf_f() { return __int_as_float(0xff800000); }
+
+__global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __grid_constant__ PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const int head = blockIdx.x;
+    const int seq = blockIdx.z;
+    const int q_tile = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);  // long tiles first
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const int row0 = p.q_offsets[seq];
+    const int t = p.q_offsets[seq + 1] - row0;
+    const int q0 = q_tile * kTileQ;
+    if (q0 >= t) return;
+    const int start = p.starts[seq];
+    const int end = start + t;
+    const int first_pos = start + q0;
+    const int last_pos = start + min(q0 + kTileQ, t) - 1;
+    const int W = static_cast<int>(p.window);
+    const int key_lo = (W != 0 && first_pos + 1 > W) ? first_pos + 1 - W : 0;
+    const int kt_lo = key_lo / kTileK, kt_hi = last_pos / kTileK;
+    const int n_tiles = kt_hi - kt_lo + 1;
+
+    const uint32_t raw = smem_u32(smem_raw);
+    uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+    Bars *bars = reinterpret_cast<Bars *>(smem + kOffBars);
+    const uint32_t smem_base = smem_u32(smem);
+
+    if (warp == 0 && lane == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < kStagesKV; ++s) {
+            mbar_init(&bars->k_full[s], 1);
+            mbar_init(&bars->k_empty[s], 1);
+            mbar_init(&bars->v_full[s], 1);
+            mbar_init(&bars->v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->s_full[b], 1);
+            mbar_init(&bars->p_full[b], 128);
+            mbar_init(&bars->pv_done[b], 1);
+        }
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    const int kv_head = head / kGroup;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(&bars->q_full, 2 * kPlaneBytes);
+            tma_load_3d(smem + kOffQhi, &p.q_hi_map, 0, head, row0 + q0, &bars->q_full);
+            tma_load_3d(smem + kOffQlo, &p.q_lo_map, 0, head, row0 + q0, &bars->q_full);
+            const int32_t *table_row = p.block_table + static_cast<size_t>(seq) * p.max_pages;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int stage = j % kStagesKV;
+                const int kt = kt_lo + j;
+                // page rows in the pool for the 8 pages of this tile (out-of-range row = zero fill)
+                int y[8];
+#pragma unroll
+                for (int pg = 0; pg < 8; ++pg) {
+                    const int lp = kt * 8 + pg;
+                    y[pg] = static_cast<int>(p.pool_rows);  // past the end of the tensor: TMA writes zeros
+                    if (lp * kPageTokens < end) {
+                        uint32_t idx = static_cast<uint32_t>(lp);
+                        if (p.ring_pages) idx %= p.ring_pages;
+                        const int32_t page = idx < p.max_pages ? table_row[idx] : -1;
+                        if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages)
+                            raise_status(p.status, kStatusBadPage);
+                        else
+                            y[pg] = (page * static_cast<int>(p.kv_heads) + kv_head) * kTileRows;
+                    }
+                }
+                if (j >= kStagesKV) ok = mbar_wait(&bars->k_empty[stage], ((j / kStagesKV) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&bars->k_full[stage], kPlaneBytes);
+#pragma unroll
+                for (int pg = 0; pg < 8; ++pg)
+                    tma_load_2d(smem + kOffK + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0, y[pg],
+                                &bars->k_full[stage]);
+                if (j >= kStagesKV) ok = mbar_wait(&bars->v_empty[stage], ((j / kStagesKV) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&bars->v_full[stage], kPlaneBytes);
+#pragma unroll
+                for (int pg = 0; pg < 8; ++pg)
+                    tma_load_2d(smem + kOffV + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0,
+                                y[pg] == static_cast<int>(p.pool_rows) ? y[pg] : y[pg] + kPageTokens,
+                                &bars->v_full[stage]);
+            }
+            if (!ok) raise_status(p.status, kStatusWaitTimeout);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileQ, kTileK, false);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true) & ~(7u << 7);  // A (P) is fp16
+            const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQhi, 16, 1024);
+            const uint64_t qlo_desc = smem_desc_sw128(smem_base + kOffQlo, 16, 1024);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            tc_fence_after();
+            auto issue_qk = [&](int j) -> bool {
+                const int stage = j % kStagesKV;
+                if (!mbar_wait(&bars->k_full[stage], (j / kStagesKV) & 1)) return false;
+                tc_fence_after();
+                const uint64_t k_desc = smem_desc_sw128(smem_base + kOffK + stage * kPlaneBytes, 16, 1024);
+                const uint32_t d = tmem + static_cast<uint32_t>(j & 1) * kTileK;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qhi_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qlo_desc + ks * 2, k_desc + ks * 2, idesc_qk, true);
+                umma_commit(&bars->s_full[j & 1]);
+                umma_commit(&bars->k_empty[stage]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+                if (!ok) break;
+                const int stage = j % kStagesKV;
+                ok = mbar_wait(&bars->p_full[j & 1], (j >> 1) & 1);
+                if (ok) ok = mbar_wait(&bars->v_full[stage], (j / kStagesKV) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t p_desc = smem_desc_sw128(smem_base + kOffP + (j & 1) * 2 * kPlaneBytes, 16, 1024);
+                const uint64_t v_desc = smem_desc_sw128(smem_base + kOffV + stage * kPlaneBytes, 1024, 1024);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    umma_bf16(tmem + kColO, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2,
+                              v_desc + ks * (2048 >> 4), idesc_pv, j > 0 || ks > 0);
+                umma_commit(&bars->pv_done[j & 1]);
+                umma_commit(&bars->v_empty[stage]);
+            }
+            if (!ok) raise_status(p.status, kStatusWaitTimeout);
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- softmax, one row per thread
+        const int quarter = warp & 3;                 // the TMEM lanes this warp can reach
+        const int row = quarter * 32 + lane;          // row of the query tile
+        const int pos = first_pos + row;              // absolute position of this query
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const int vis_lo = (W != 0 && pos + 1 > W) ? pos + 1 - W : 0;
+        float m = neg_inf_f(), l = 0.f;
+        bool ok = true;
+        uint8_t *p_row_base = smem + kOffP + row * 128;
+        const int sw = row & 7;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
+            ok = mbar_wait(&bars->s_full[b], (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t s[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_x32(tmem + lane_addr + b * kTileK + c * 32, s[c]);
+            tmem_wait_ld();
+            const int kt = kt_lo + j;
+            const int key0 = kt * kTileK;
+            const bool edge = (key0 + kTileK - 1 > first_pos) || (W != 0 && key0 + W <= last_pos);
+            if (edge) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c * 32 + i;
+                        if (key > pos || key < vis_lo) s[c][i] = 0xff800000u;
+                    }
+            }
+            float mx = neg_inf_f();
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            const float m_cand = fmaxf(m, mx * p.scale_log2e);
+            // keep the old maximum unless it moved by more than 2^8: fewer trips through TMEM
+            const bool move = (m_cand > m + kRescaleThreshold) || (m == neg_inf_f() && m_cand > m);
+            const float m_new = move ? m_cand : m;
+            const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
+            const float alpha = move ? ex2(m - m_use) : 1.0f;
+            l *= alpha;
+            m = m_new;
+            if (j > 0) {
+                ok = mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, move)) {
+#pragma unroll
+                    for (int hcol = 0; hcol < 2; ++hcol) {
+                        uint32_t o[32];
+                        tmem_ld_x32(tmem + lane_addr + kColO + hcol * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_x32(tmem + lane_addr + kColO + hcol * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // P = exp2(s * scale - m) as fp16, 8 keys (16 bytes) at a time, into the swizzled tile
+            uint8_t *p_row = p_row_base + b * 2 * kPlaneBytes;
+            float l_add = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = ex2(fmaf(__uint_as_float(s[c][q8 * 8 + 2 * e]), p.scale_log2e, -m_use));
+                        const float p1 = ex2(fmaf(__uint_as_float(s[c][q8 * 8 + 2 * e + 1]), p.scale_log2e, -m_use));
+                        w[e] = pack_f16x2(p0, p1);
+                        l_add += p0 + p1;
+                    }
+                    const int chunk = c * 4 + q8;           // 16 chunks of 8 keys
+                    uint8_t *dst = p_row + (chunk >> 3) * kPlaneBytes + (((chunk & 7) ^ sw) << 4);
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            l += l_add;
+            fence_proxy_async();      // make the P stores visible to the tensor core's reads
+            tc_fence_before();
+            mbar_arrive(&bars->p_full[b]);
+        }
+        if (ok) {
+            ok = mbar_wait(&bars->pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float sink2 = p.sinks ? p.sinks[head] * 1.4426950408889634f : neg_inf_f();
+            const float Mt = fmaxf(m, sink2);
+            const float e = m == neg_inf_f() ? 0.f : ex2(m - Mt);
+            const float total = l * e + (p.sinks ? ex2(sink2 - Mt) : 0.f);
+            const float inv = total > 0.f ? e / total : 0.f;
+            uint16_t *out_row = p.out + (static_cast<size_t>(row0 + q0 + row) * p.heads + head) * kHeadDim;
+#pragma unroll
+            for (int hcol = 0; hcol < 2; ++hcol) {
+                uint32_t o[32];
+                tmem_ld_x32(tmem + lane_addr + kColO + hcol * 32, o);
+                tmem_wait_ld();
+                if (q0 + row < t) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v = make_uint4(
+                            pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
+                            pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                            pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
+                            pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+                        *reinterpret_cast<uint4 *>(out_row + hcol * 32 + i) = v;
+                    }
+                }
+            }
+        } else {
+            if (lane == 0) raise_status(p.status, kStatusWaitTimeout);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace
+
+void launch_prefill(const PrefillParams &p, cudaStream_t stream) {
+    cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
+    dim3 grid(p.heads, (p.max_t + kTileQ - 1) / kTileQ, p.seqs);
+    prefill_kernel<<<grid, kThreadsPrefill, kPrefillSmem, stream>>>(p);
+}
+
+}  // namespace cc

@@ -120,4 +120,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2_fast(float lo, float hi) {
     return r;
 }
 
+// Two floats to packed fp16 (round to nearest), `lo` in the low half.
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 }  // namespace cc

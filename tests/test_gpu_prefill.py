@@ -1,0 +1,122 @@
+"""Prefill attention (tcgen05/TMEM kernel) against the CPU oracle, through the C ABI.
+
+Same gate as decode: bf16 output vs the unrounded f32 output of the oracle in its bf16-cache
+mode, max abs <= 1e-2 and cosine >= 0.9999; the figure against the f32-cache (reference-faithful)
+mode is printed beside it."""
+import numpy as np
+import pytest
+
+from loadngo_b200.layer import PagedAttentionLayer
+from oracle import oracle
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+MAX_ABS, MIN_COS = 1e-2, 0.9999
+D = 64
+
+
+def bits(x):
+    return oracle.f32_to_bf16_bits(x)
+
+
+def widen(b):
+    return oracle.bf16_bits_to_f32(b)
+
+
+@pytest.mark.parametrize("window", [0, 128])
+def test_config1_prefill_matches_the_oracle(gpu, window):
+    """256 positions in one pass (batch 1, 64 heads over 8), full-causal and 128-window."""
+    q, k, v, sinks = helpers.config1_inputs(320)
+    rope = oracle.Rope()
+    ref_b = oracle.Session(64, 8, D, 320, window=window, sinks=sinks, rope=rope, cache_bf16=True)
+    ref_f = oracle.Session(64, 8, D, 320, window=window, sinks=sinks, rope=rope)
+    want_b, _ = ref_b.feed(q[:256], k[:256], v[:256], threads=8)
+    want_f, _ = ref_f.feed(q[:256], k[:256], v[:256], threads=8)
+    layer = PagedAttentionLayer(gpu, seqs=1, max_context=320, max_new=256, window=window, sinks=sinks,
+                                rng=np.random.default_rng(3))
+    got = widen(layer.prefill(bits(q[:256]), bits(k[:256]), bits(v[:256]), [256]))
+    err_b, cos_b = helpers.errors(got, want_b)
+    err_f, cos_f = helpers.errors(got, want_f)
+    print(f"\nconfig-1 prefill window={window}: vs bf16-cache oracle max_abs={err_b:.5f} cos={cos_b:.7f}; "
+          f"vs f32-cache oracle max_abs={err_f:.5f} cos={cos_f:.7f}")
+    assert err_b <= MAX_ABS and cos_b >= MIN_COS
+    assert cos_f >= MIN_COS
+    # then the 64 decode steps of the same configuration continue from the prefilled cache
+    for p in range(256, 320):
+        got1 = widen(layer.decode_step(bits(q[p:p + 1]), bits(k[p:p + 1]), bits(v[p:p + 1])))
+        want1, _ = ref_b.feed(q[p:p + 1], k[p:p + 1], v[p:p + 1])
+        assert helpers.errors(got1, want1)[0] <= MAX_ABS
+    layer.free()
+
+
+@pytest.mark.parametrize("window", [0, 128])
+def test_ragged_passes_after_a_cache(gpu, window):
+    """Several sequences, each with a different number of cached and of new positions: partial
+    query tiles, passes that start in the middle of a page and of a key tile, one-position
+    passes, windows that begin before and inside the first key tile."""
+    rng = np.random.default_rng(17)
+    cached = [0, 5, 300, 127, 1000, 64]
+    new = [1, 33, 77, 129, 260, 512]
+    sinks = rng.standard_normal(64).astype(np.float32) * 2
+    rope = oracle.Rope()
+    seqs = len(cached)
+    layer = PagedAttentionLayer(gpu, seqs=seqs, max_context=1600, max_new=max(sum(new), sum(cached)), window=window,
+                                sinks=sinks, rng=rng)
+    refs, q_new, k_new, v_new, want = [], [], [], [], []
+    # the past of every sequence goes in with one append-only batch
+    qs, ks, vs, pos, ids = [], [], [], [], []
+    for s in range(seqs):
+        ref = oracle.Session(64, 8, D, cached[s] + new[s], window=window, sinks=sinks, rope=rope, cache_bf16=True)
+        n = cached[s]
+        q = oracle.round_bf16(rng.standard_normal((n, 64, D)).astype(np.float32))
+        k = oracle.round_bf16(rng.standard_normal((n, 8, D)).astype(np.float32))
+        v = oracle.round_bf16(rng.standard_normal((n, 8, D)).astype(np.float32))
+        if n:
+            ref.feed(q, k, v, threads=8)
+        refs.append(ref)
+        qs.append(q); ks.append(k); vs.append(v)
+        pos.append(np.arange(n)); ids.append(np.full(n, s))
+        layer.cache.reserve(s, n)
+    layer.cache.flush_table()
+    total_cached = sum(cached)
+    layer._stage(bits(np.concatenate(qs)), bits(np.concatenate(ks)), bits(np.concatenate(vs)),
+                 np.concatenate(pos), np.concatenate(ids))
+    batch = gpu.batch(layer.buffers())
+    layer.record_append(batch, total_cached)
+    assert not isinstance(batch.run().gpu_time, Exception)
+    for s in range(seqs):
+        q = oracle.round_bf16(rng.standard_normal((new[s], 64, D)).astype(np.float32))
+        k = oracle.round_bf16(rng.standard_normal((new[s], 8, D)).astype(np.float32))
+        v = oracle.round_bf16(rng.standard_normal((new[s], 8, D)).astype(np.float32))
+        out, _ = refs[s].feed(q, k, v, threads=8)
+        q_new.append(q); k_new.append(k); v_new.append(v); want.append(out)
+    got = widen(layer.prefill(bits(np.concatenate(q_new)), bits(np.concatenate(k_new)), bits(np.concatenate(v_new)), new))
+    at = 0
+    for s in range(seqs):
+        err, cos = helpers.errors(got[at:at + new[s]], want[s])
+        assert not np.isnan(got[at:at + new[s]]).any()
+        assert err <= MAX_ABS and cos >= MIN_COS, f"sequence {s} (cached {cached[s]}, new {new[s]}): {err} {cos}"
+        at += new[s]
+    layer.free()
+
+
+def test_long_pass_skips_tiles_outside_the_window(gpu):
+    """2 x 2048 positions: the window layer visits two or three key tiles per query tile, the
+    full layer up to sixteen; both against the oracle."""
+    rng = np.random.default_rng(23)
+    T = 2048
+    sinks = rng.standard_normal(64).astype(np.float32)
+    rope = oracle.Rope()
+    q = oracle.round_bf16(rng.standard_normal((2 * T, 64, D)).astype(np.float32))
+    k = oracle.round_bf16(rng.standard_normal((2 * T, 8, D)).astype(np.float32))
+    v = oracle.round_bf16(rng.standard_normal((2 * T, 8, D)).astype(np.float32))
+    for window in (128, 0):
+        layer = PagedAttentionLayer(gpu, seqs=2, max_context=T, max_new=2 * T, window=window, sinks=sinks, rng=rng)
+        got = widen(layer.prefill(bits(q), bits(k), bits(v), [T, T]))
+        for s in range(2):
+            ref = oracle.Session(64, 8, D, T, window=window, sinks=sinks, rope=rope, cache_bf16=True)
+            want, _ = ref.feed(q[s * T:(s + 1) * T], k[s * T:(s + 1) * T], v[s * T:(s + 1) * T], threads=16)
+            err, cos = helpers.errors(got[s * T:(s + 1) * T], want)
+            print(f"\nprefill 2x{T} window={window} seq {s}: max_abs={err:.5f} cos={cos:.7f}")
+            assert err <= MAX_ABS and cos >= MIN_COS
+        layer.free()
