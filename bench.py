@@ -424,6 +424,20 @@ def run_gpu(args):
 
     gpu = compute.Gpu(local)
     heads_here = shard_kv_heads(KV_HEADS, world, rank)
+    if args.only_prefill:
+        # the prefill section alone (used for profiling that kernel): prints its numbers and stops
+        pb = PrefillBench(gpu, len(heads_here))
+        tpeak, tpeak_kind = measured_tensor_peak()
+        out = {"prefill_only": True, "peak_tflops": tpeak, "peak_source": tpeak_kind}
+        for li, name in ((0, "full_causal"), (1, "window_128")):
+            pb.run(li, 2)
+            sec = pb.run(li, max(2, min(args.steps, 20)))
+            tf = pb.flops(WINDOW if li else 0) / sec / 1e12
+            out[name] = {"ms": sec * 1e3, "tflops": tf, "frac_of_peak": tf / tpeak}
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        pb.free()
+        return
     lens = draw_lengths(SEQS_PER_GPU * world)
     total_steps = args.warmup + args.steps
     bench = DecodeBench(gpu, lens, len(heads_here), total_steps * 3 + 2)
@@ -517,6 +531,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (config 3) section")
+    ap.add_argument("--only-prefill", action="store_true", help="run only the prefill (config 3) section")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU baseline work")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -14,9 +14,9 @@
 //   warp 1  one thread issues tcgen05.mma: S = Qhi K^T + Qlo K^T (M128 N128 K64 twice) into one of
 //           two S buffers in TMEM, and O += P V (M128 N64 K128) into the O accumulator in TMEM;
 //   warps 2-5  softmax: one thread per query row reads its S row from TMEM, masks edge tiles,
-//           keeps the running maximum and sum, writes P as fp16 (11 significant bits; the
-//           weights lie in [0, 2^8]) into shared memory in the swizzled K-major layout the P V
-//           product reads (tcgen05 kind::f16 multiplies an fp16 A by a bf16 B), and rescales its O row in TMEM when
+//           keeps the running maximum and sum, writes P as bf16 into shared memory in the
+//           swizzled K-major layout the P V product reads (an fp16 P against bf16 V is not a
+//           legal kind::f16 pairing: both operands must share a format), and rescales its O row in TMEM when
 //           its maximum moved by more than 2^8; at the end it folds the sink in, normalises and
 //           stores 128 bytes of bf16 output.
 // S is double-buffered so that S(j+1) = Q K(j+1)^T is computed while the softmax of tile j runs.
@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileQ, kTileK, false);
-            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true) & ~(7u << 7);  // A (P) is fp16
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true);
             const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQhi, 16, 1024);
             const uint64_t qlo_desc = smem_desc_sw128(smem_base + kOffQlo, 16, 1024);
             bool ok = mbar_wait(&bars->q_full, 0);
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                     tmem_wait_st();
                 }
             }
-            // P = exp2(s * scale - m) as fp16, 8 keys (16 bytes) at a time, into the swizzled tile
+            // P = exp2(s * scale - m) as bf16, 8 keys (16 bytes) at a time, into the swizzled tile
             uint8_t *p_row = p_row_base + b * 2 * kPlaneBytes;
             float l_add = 0.f;
 #pragma unroll
@@ -273,8 +273,9 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                     for (int e = 0; e < 4; ++e) {
                         const float p0 = ex2(fmaf(__uint_as_float(s[c][q8 * 8 + 2 * e]), p.scale_log2e, -m_use));
                         const float p1 = ex2(fmaf(__uint_as_float(s[c][q8 * 8 + 2 * e + 1]), p.scale_log2e, -m_use));
-                        w[e] = pack_f16x2(p0, p1);
-                        l_add += p0 + p1;
+                        w[e] = pack_bf16x2_fast(p0, p1);
+                        // the sum uses the rounded weights, the ones the product will use
+                        l_add += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
                     }
                     const int chunk = c * 4 + q8;           // 16 chunks of 8 keys
                     uint8_t *dst = p_row + (chunk >> 3) * kPlaneBytes + (((chunk & 7) ^ sw) << 4);

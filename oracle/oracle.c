@@ -258,3 +258,15 @@ int oracle_max_threads(void) {
     long n = sysconf(_SC_NPROCESSORS_ONLN);
     return n > 0 ? (int)n : 1;
 }
+
+/* The deterministic inputs of the reference's kernel tests: xorshift64, values in [-1, 1)
+ * (metal-compute/tests/attention_grouped.rs:25-35). */
+void oracle_xorshift_values(uint64_t seed, long n, float *out) {
+    uint64_t s = seed | 1;
+    for (long i = 0; i < n; ++i) {
+        s ^= s << 13;
+        s ^= s >> 7;
+        s ^= s << 17;
+        out[i] = (float)(s >> 40) / (float)(1ull << 23) - 1.0f;
+    }
+}

@@ -54,6 +54,7 @@ def lib() -> ctypes.CDLL:
         L.oracle_rms_norm.argtypes = [_f32p, _f32p, ctypes.c_float, ctypes.c_long, _f32p]
         L.oracle_bf16_matvec.argtypes = [_u16p, ctypes.c_long, ctypes.c_long, _f32p, _f32p]
         L.oracle_max_threads.restype = ctypes.c_int
+        L.oracle_xorshift_values.argtypes = [ctypes.c_uint64, ctypes.c_long, _f32p]
         _lib = L
     return _lib
 
@@ -81,6 +82,13 @@ class Rope:
         out = np.zeros((t, self.head_dim // 2, 2), np.float32)
         lib().oracle_rope_table(inv, scale, self.head_dim // 2, start, t, out)
         return out
+
+
+def xorshift_values(seed: int, n: int) -> np.ndarray:
+    """`values(seed, n)` of metal-compute/tests/attention_grouped.rs:25-35."""
+    out = np.zeros(n, np.float32)
+    lib().oracle_xorshift_values(seed, n, out)
+    return out
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -157,17 +165,18 @@ def attention_f64(q, k, v, *, start, window, scale, sinks=None):
     k = np.asarray(k, np.float64)
     v = np.asarray(v, np.float64)
     t, heads, dim = q.shape
-    group = heads // k.shape[1]
+    kv_heads = k.shape[1]
+    group = heads // kv_heads
     out = np.zeros((t, heads, dim), np.float64)
+    sink = np.full(heads, -np.inf) if sinks is None else np.asarray(sinks, np.float64)
     for i in range(t):
         last = start + i
         first = max(0, last + 1 - window) if window > 0 else 0
-        for h in range(heads):
-            g = h // group
-            s = (k[first:last + 1, g] @ q[i, h]) * float(scale)
-            sink = -np.inf if sinks is None else float(sinks[h])
-            m = max(sink, s.max())
-            e = np.exp(s - m)
-            z = e.sum() + np.exp(sink - m)
-            out[i, h] = (e / z) @ v[first:last + 1, g]
+        for g in range(kv_heads):
+            hs = slice(g * group, (g + 1) * group)
+            s = (q[i, hs] @ k[first:last + 1, g].T) * float(scale)
+            m = np.maximum(s.max(axis=1), sink[hs])
+            e = np.exp(s - m[:, None])
+            z = e.sum(axis=1) + np.exp(sink[hs] - m)
+            out[i, hs] = (e / z[:, None]) @ v[first:last + 1, g]
     return out.astype(np.float32)

@@ -11,15 +11,7 @@ PAGE, D = 16, 64
 def xorshift_values(seed: int, n: int) -> np.ndarray:
     """The deterministic inputs of the reference's kernel tests, values in [-1, 1)
     (metal-compute/tests/attention_grouped.rs:25-35)."""
-    s = (seed | 1) & 0xFFFFFFFFFFFFFFFF
-    out = np.empty(n, np.float32)
-    mask = 0xFFFFFFFFFFFFFFFF
-    for i in range(n):
-        s ^= (s << 13) & mask
-        s ^= s >> 7
-        s ^= (s << 17) & mask
-        out[i] = np.float32(s >> 40) / np.float32(1 << 23) - np.float32(1.0)
-    return out
+    return oracle.xorshift_values(seed, n)
 
 
 def config1_inputs(positions: int = 320, heads: int = 64, kv_heads: int = 8, seed: int = 0):
