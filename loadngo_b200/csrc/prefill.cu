@@ -8,17 +8,23 @@
 // denominator only (model.rs:449-455).  The new positions' keys and values are already in
 // the paged cache (the fused RoPE + append kernel ran first).
 //
-// One CTA = 128 queries of one head.  Six warps, three roles:
+// One CTA = 128 queries of one head.  Ten warps, three roles:
 //   warp 0  producer: TMA loads of the Q tile (hi and lo planes) and, per 128-key tile, eight
-//           16-key pages of K and of V, found through the block table, into 3-stage rings;
+//           16-key pages of K and of V, found through the block table, into 3-stage rings
+//           (sixteen lanes look up and issue one page each);
 //   warp 1  one thread issues tcgen05.mma: S = Qhi K^T + Qlo K^T (M128 N128 K64 twice) into one of
-//           two S buffers in TMEM, and O += P V (M128 N64 K128) into the O accumulator in TMEM;
-//   warps 2-5  softmax: one thread per query row reads its S row from TMEM, masks edge tiles,
-//           keeps the running maximum and sum, writes P as bf16 into shared memory in the
-//           swizzled K-major layout the P V product reads (an fp16 P against bf16 V is not a
-//           legal kind::f16 pairing: both operands must share a format), and rescales its O row in TMEM when
-//           its maximum moved by more than 2^8; at the end it folds the sink in, normalises and
-//           stores 128 bytes of bf16 output.
+//           two S buffers in TMEM, O += P V (M128 N64 K128) into the O accumulator in TMEM, and
+//           L += P 1 (M128 N16 K128, B = a tile of ones) so that each row's softmax denominator
+//           is summed by the tensor core from exactly the weights the P V product uses;
+//   warps 2-9  softmax: two threads per query row, each owning 64 of the tile's 128 keys.  A
+//           thread reads its half of the S row from TMEM, masks edge tiles, shares the row
+//           maximum with its partner through shared memory, writes P = exp2(s - m) as bf16
+//           into shared memory in the swizzled K-major layout the P V product reads, and
+//           rescales its half of the O row (and the L column) in TMEM when the maximum moved
+//           by more than 2^8; at the end it folds the sink in, normalises and stores 64 bytes
+//           of bf16 output.  Two softmax warps per scheduler hide each other's TMEM and MUFU
+//           latencies; with the sums on the tensor core a key costs one FMA, one exp2 and half
+//           a convert per thread.
 // S is double-buffered so that S(j+1) = Q K(j+1)^T is computed while the softmax of tile j runs.
 // Tiles entirely outside a query tile's causal / window range are never visited (the loop
 // bounds exclude them, as kernels.metal:631-634 does); only edge tiles are masked per element.
@@ -34,17 +40,21 @@ namespace {
 
 constexpr int kTileQ = 128, kTileK = 128;
 constexpr int kStagesKV = 3;
-constexpr int kThreadsPrefill = 192;
+constexpr int kThreadsPrefill = 320;
+constexpr int kSoftmaxThreads = 256;
 constexpr int kPlaneBytes = kTileQ * kHeadDim * 2;          // 16 KiB: 128 rows of 128 bytes
 constexpr int kOffQhi = 0;
 constexpr int kOffQlo = kPlaneBytes;
 constexpr int kOffK = 2 * kPlaneBytes;
 constexpr int kOffV = kOffK + kStagesKV * kPlaneBytes;
 constexpr int kOffP = kOffV + kStagesKV * kPlaneBytes;      // 2 buffers of 128 x 128 bf16
-constexpr int kOffBars = kOffP + 2 * 2 * kPlaneBytes;
+constexpr int kOffOnes = kOffP + 2 * 2 * kPlaneBytes;       // 16 rows x 128 bytes of bf16 1.0
+constexpr int kOffXchg = kOffOnes + 2048;                   // [2 tiles in flight][2 halves][128 rows] f32
+constexpr int kOffBars = kOffXchg + 2 * 2 * 128 * 4;
 constexpr int kPrefillSmem = kOffBars + 256 + 1024;
-constexpr uint32_t kTmemCols = 512;                         // S0 0-127, S1 128-255, O 256-319
+constexpr uint32_t kTmemCols = 512;                         // S0 0-127, S1 128-255, O 256-319, L 320-335
 constexpr uint32_t kColO = 256;
+constexpr uint32_t kColL = 320;
 constexpr float kRescaleThreshold = 8.0f;                   // log2 domain
 
 struct Bars {
@@ -92,7 +102,7 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bars->s_full[b], 1);
-            mbar_init(&bars->p_full[b], 128);
+            mbar_init(&bars->p_full[b], kSoftmaxThreads);
             mbar_init(&bars->pv_done[b], 1);
         }
         mbar_fence_init();
@@ -102,6 +112,9 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         tmem_alloc(&bars->tmem_base, kTmemCols);
         tmem_relinquish();
     }
+    // the ones tile: any arrangement of ones is the same tile, so the swizzle does not matter
+    for (int i = tid; i < 2048 / 4; i += kThreadsPrefill) reinterpret_cast<uint32_t *>(smem + kOffOnes)[i] = 0x3f803f80u;
+    fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -111,55 +124,61 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
+        // Lanes 0-7 each bring one 16-key page of K per tile, lanes 8-15 the same page of V: the
+        // sixteen block-table look-ups and TMA issues of a tile go out side by side instead of
+        // one after the other from a single thread.
         if (lane == 0) {
-            bool ok = true;
             mbar_expect_tx(&bars->q_full, 2 * kPlaneBytes);
             tma_load_3d(smem + kOffQhi, &p.q_hi_map, 0, head, row0 + q0, &bars->q_full);
             tma_load_3d(smem + kOffQlo, &p.q_lo_map, 0, head, row0 + q0, &bars->q_full);
-            const int32_t *table_row = p.block_table + static_cast<size_t>(seq) * p.max_pages;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int stage = j % kStagesKV;
-                const int kt = kt_lo + j;
-                // page rows in the pool for the 8 pages of this tile (out-of-range row = zero fill)
-                int y[8];
-#pragma unroll
-                for (int pg = 0; pg < 8; ++pg) {
-                    const int lp = kt * 8 + pg;
-                    y[pg] = static_cast<int>(p.pool_rows);  // past the end of the tensor: TMA writes zeros
-                    if (lp * kPageTokens < end) {
-                        uint32_t idx = static_cast<uint32_t>(lp);
-                        if (p.ring_pages) idx %= p.ring_pages;
-                        const int32_t page = idx < p.max_pages ? table_row[idx] : -1;
-                        if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages)
-                            raise_status(p.status, kStatusBadPage);
-                        else
-                            y[pg] = (page * static_cast<int>(p.kv_heads) + kv_head) * kTileRows;
-                    }
-                }
-                if (j >= kStagesKV) ok = mbar_wait(&bars->k_empty[stage], ((j / kStagesKV) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(&bars->k_full[stage], kPlaneBytes);
-#pragma unroll
-                for (int pg = 0; pg < 8; ++pg)
-                    tma_load_2d(smem + kOffK + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0, y[pg],
-                                &bars->k_full[stage]);
-                if (j >= kStagesKV) ok = mbar_wait(&bars->v_empty[stage], ((j / kStagesKV) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(&bars->v_full[stage], kPlaneBytes);
-#pragma unroll
-                for (int pg = 0; pg < 8; ++pg)
-                    tma_load_2d(smem + kOffV + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0,
-                                y[pg] == static_cast<int>(p.pool_rows) ? y[pg] : y[pg] + kPageTokens,
-                                &bars->v_full[stage]);
-            }
-            if (!ok) raise_status(p.status, kStatusWaitTimeout);
         }
+        const int32_t *table_row = p.block_table + static_cast<size_t>(seq) * p.max_pages;
+        const int pg = lane & 7;
+        const bool is_v = lane >= 8;
+        // row of this lane's page in the pool (a row past the end of the tensor = TMA writes zeros)
+        auto lookup = [&](int kt) -> int {
+            const int lp = kt * 8 + pg;
+            int y = static_cast<int>(p.pool_rows);
+            if (lane < 16 && lp * kPageTokens < end) {
+                uint32_t idx = static_cast<uint32_t>(lp);
+                if (p.ring_pages) idx %= p.ring_pages;
+                const int32_t page = idx < p.max_pages ? table_row[idx] : -1;
+                if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages)
+                    raise_status(p.status, kStatusBadPage);
+                else
+                    y = (page * static_cast<int>(p.kv_heads) + kv_head) * kTileRows + (is_v ? kPageTokens : 0);
+            }
+            return y;
+        };
+        bool ok = true;
+        int y_next = lookup(kt_lo);
+        for (int j = 0; j < n_tiles; ++j) {
+            const int stage = j % kStagesKV;
+            const int y = y_next;
+            if (j + 1 < n_tiles) y_next = lookup(kt_lo + j + 1);   // in flight while this tile is issued
+            if (lane == 0) {
+                if (j >= kStagesKV) ok = mbar_wait(&bars->k_empty[stage], ((j / kStagesKV) - 1) & 1);
+                if (ok) mbar_expect_tx(&bars->k_full[stage], kPlaneBytes);
+            } else if (lane == 8) {
+                if (j >= kStagesKV) ok = mbar_wait(&bars->v_empty[stage], ((j / kStagesKV) - 1) & 1);
+                if (ok) mbar_expect_tx(&bars->v_full[stage], kPlaneBytes);
+            }
+            ok = __all_sync(0xffffffffu, ok);   // also orders the expect_tx before the loads below
+            if (!ok) break;
+            if (lane < 8)
+                tma_load_2d(smem + kOffK + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->k_full[stage]);
+            else if (lane < 16)
+                tma_load_2d(smem + kOffV + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->v_full[stage]);
+        }
+        if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
         __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileQ, kTileK, false);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true);
+            constexpr uint32_t idesc_l = umma_idesc_bf16(kTileQ, 16, false);
+            const uint64_t ones_desc = smem_desc_sw128(smem_base + kOffOnes, 16, 1024);
             const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQhi, 16, 1024);
             const uint64_t qlo_desc = smem_desc_sw128(smem_base + kOffQlo, 16, 1024);
             bool ok = mbar_wait(&bars->q_full, 0);
@@ -193,6 +212,10 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                 for (int ks = 0; ks < 8; ++ks)
                     umma_bf16(tmem + kColO, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2,
                               v_desc + ks * (2048 >> 4), idesc_pv, j > 0 || ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    umma_bf16(tmem + kColL, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2, ones_desc, idesc_l,
+                              j > 0 || ks > 0);
                 umma_commit(&bars->pv_done[j & 1]);
                 umma_commit(&bars->v_empty[stage]);
             }
@@ -200,31 +223,34 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         }
         __syncwarp();
     } else {
-        // ---------------------------------------------------------------- softmax, one row per thread
+        // ------------------------------------------------- softmax, two threads per row (64 keys each)
         const int quarter = warp & 3;                 // the TMEM lanes this warp can reach
+        const int half = (warp - 2) >> 2;             // which 64 of the tile's 128 keys, which 32 of O's 64 columns
         const int row = quarter * 32 + lane;          // row of the query tile
         const int pos = first_pos + row;              // absolute position of this query
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const int vis_lo = (W != 0 && pos + 1 > W) ? pos + 1 - W : 0;
-        float m = neg_inf_f(), l = 0.f;
+        float *xchg = reinterpret_cast<float *>(smem + kOffXchg);
+        float m = neg_inf_f();
         bool ok = true;
-        uint8_t *p_row_base = smem + kOffP + row * 128;
+        uint8_t *p_row_base = smem + kOffP + half * kPlaneBytes + row * 128;
         const int sw = row & 7;
+        const float scale = p.scale_log2e;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
             ok = mbar_wait(&bars->s_full[b], (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            uint32_t s[4][32];
+            uint32_t s[2][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_x32(tmem + lane_addr + b * kTileK + c * 32, s[c]);
+            for (int c = 0; c < 2; ++c) tmem_ld_x32(tmem + lane_addr + b * kTileK + half * 64 + c * 32, s[c]);
             tmem_wait_ld();
             const int kt = kt_lo + j;
-            const int key0 = kt * kTileK;
-            const bool edge = (key0 + kTileK - 1 > first_pos) || (W != 0 && key0 + W <= last_pos);
+            const int key0 = kt * kTileK + half * 64;
+            const bool edge = (kt * kTileK + kTileK - 1 > first_pos) || (W != 0 && kt * kTileK + W <= last_pos);
             if (edge) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = key0 + c * 32 + i;
@@ -233,56 +259,68 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
             }
             float mx = neg_inf_f();
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
-            const float m_cand = fmaxf(m, mx * p.scale_log2e);
+                for (int i = 0; i < 32; i += 2)
+                    mx = fmaxf(mx, fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
+            // the row maximum over both halves: through shared memory, one named barrier per tile
+            xchg[(b * 2 + half) * 128 + row] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * 128 + row]);
+            const float m_cand = fmaxf(m, mx * scale);
             // keep the old maximum unless it moved by more than 2^8: fewer trips through TMEM
             const bool move = (m_cand > m + kRescaleThreshold) || (m == neg_inf_f() && m_cand > m);
             const float m_new = move ? m_cand : m;
             const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
             const float alpha = move ? ex2(m - m_use) : 1.0f;
-            l *= alpha;
             m = m_new;
-            if (j > 0) {
+            // Only a rescale has to wait for the previous tile's P V product; the common case goes
+            // straight on to its exponentials while that product is still running.
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
                 ok = mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, move)) {
+                {
+                    uint32_t o[32];
+                    tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int hcol = 0; hcol < 2; ++hcol) {
-                        uint32_t o[32];
-                        tmem_ld_x32(tmem + lane_addr + kColO + hcol * 32, o);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_x32(tmem + lane_addr + kColO + half * 32, o);
+                    if (half == 0) {   // the row sum lives in column kColL; one of the two threads scales it
+                        uint32_t lsum;
+                        tmem_ld_x1(tmem + lane_addr + kColL, lsum);
                         tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_x32(tmem + lane_addr + kColO + hcol * 32, o);
+                        lsum = __float_as_uint(__uint_as_float(lsum) * alpha);
+                        tmem_st_x1(tmem + lane_addr + kColL, lsum);
                     }
                     tmem_wait_st();
                 }
             }
+            // the P buffer of this parity was last read by the product of tile j - 2
+            if (j >= 2) {
+                ok = mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1);
+                if (!ok) break;
+            }
             // P = exp2(s * scale - m) as bf16, 8 keys (16 bytes) at a time, into the swizzled tile
             uint8_t *p_row = p_row_base + b * 2 * kPlaneBytes;
-            float l_add = 0.f;
+            const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
 #pragma unroll
                 for (int q8 = 0; q8 < 4; ++q8) {
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float p0 = ex2(fmaf(__uint_as_float(s[c][q8 * 8 + 2 * e]), p.scale_log2e, -m_use));
-                        const float p1 = ex2(fmaf(__uint_as_float(s[c][q8 * 8 + 2 * e + 1]), p.scale_log2e, -m_use));
-                        w[e] = pack_bf16x2_fast(p0, p1);
-                        // the sum uses the rounded weights, the ones the product will use
-                        l_add += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
+                        const float2 x = ffma2(make_float2(__uint_as_float(s[c][q8 * 8 + 2 * e]),
+                                                           __uint_as_float(s[c][q8 * 8 + 2 * e + 1])),
+                                               scale2, neg_m2);
+                        w[e] = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
                     }
-                    const int chunk = c * 4 + q8;           // 16 chunks of 8 keys
-                    uint8_t *dst = p_row + (chunk >> 3) * kPlaneBytes + (((chunk & 7) ^ sw) << 4);
-                    *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    const int chunk = c * 4 + q8;           // 8 chunks of 8 keys in this thread's half
+                    *reinterpret_cast<uint4 *>(p_row + ((chunk ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
-            l += l_add;
             fence_proxy_async();      // make the P stores visible to the tensor core's reads
             tc_fence_before();
             mbar_arrive(&bars->p_full[b]);
@@ -292,27 +330,27 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         }
         if (ok) {
             tc_fence_after();
+            uint32_t lsum;
+            tmem_ld_x1(tmem + lane_addr + kColL, lsum);
+            uint32_t o[32];
+            tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
+            tmem_wait_ld();
+            const float l = __uint_as_float(lsum);
             const float sink2 = p.sinks ? p.sinks[head] * 1.4426950408889634f : neg_inf_f();
             const float Mt = fmaxf(m, sink2);
             const float e = m == neg_inf_f() ? 0.f : ex2(m - Mt);
             const float total = l * e + (p.sinks ? ex2(sink2 - Mt) : 0.f);
             const float inv = total > 0.f ? e / total : 0.f;
-            uint16_t *out_row = p.out + (static_cast<size_t>(row0 + q0 + row) * p.heads + head) * kHeadDim;
+            if (q0 + row < t) {
+                uint16_t *out_row =
+                    p.out + (static_cast<size_t>(row0 + q0 + row) * p.heads + head) * kHeadDim + half * 32;
 #pragma unroll
-            for (int hcol = 0; hcol < 2; ++hcol) {
-                uint32_t o[32];
-                tmem_ld_x32(tmem + lane_addr + kColO + hcol * 32, o);
-                tmem_wait_ld();
-                if (q0 + row < t) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 v = make_uint4(
-                            pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
-                            pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
-                            pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
-                            pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
-                        *reinterpret_cast<uint4 *>(out_row + hcol * 32 + i) = v;
-                    }
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v = make_uint4(pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
+                                         pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                                         pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
+                                         pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+                    *reinterpret_cast<uint4 *>(out_row + i) = v;
                 }
             }
         } else {

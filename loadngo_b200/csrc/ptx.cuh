@@ -44,12 +44,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Polls at most `kSpinLimit` times (each try_wait already blocks for a hardware-defined
-// slice of time), then gives up.  Returns false on give-up.
-constexpr uint32_t kSpinLimit = 1u << 22;
+// Waits for the phase with the given parity, but never for long: it gives up after about a
+// second of SM clock cycles (or `kSpinLimit` polls, whichever comes first) and returns false,
+// so that a protocol error shows up as a status code and not as a hung GPU.
+constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr long long kWaitCycles = 2000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long began = clock64();
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && clock64() - began > kWaitCycles) return false;
     }
     return false;
 }
