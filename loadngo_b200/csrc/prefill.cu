@@ -8,24 +8,26 @@
 // denominator only (model.rs:449-455).  The new positions' keys and values are already in
 // the paged cache (the fused RoPE + append kernel ran first).
 //
-// One CTA = 128 queries of one head.  Ten warps, three roles:
-//   warp 0  producer: TMA loads of the Q tile (hi and lo planes) and, per 128-key tile, eight
-//           16-key pages of K and of V, found through the block table, into 3-stage rings
-//           (sixteen lanes look up and issue one page each);
+// A work item = 128 queries of one head.  CTAs are persistent (one per SM): each walks its own
+// fixed sequence of items (heaviest first, the 8 heads of a KV group next to each other so that
+// they share K and V through L2), and its pipelines run on across item boundaries: while the
+// softmax warps finish one item, the producer is already loading the next item's Q, K and V and
+// the tensor core is already computing its first scores.  Ten warps, three roles:
+//   warp 0  producer: TMA loads of the Q tile (hi and lo planes, double-buffered) and, per
+//           128-key tile, eight 16-key pages of K and of V, found through the block table, into
+//           rings (sixteen lanes look up and issue one page each);
 //   warp 1  one thread issues tcgen05.mma: S = Qhi K^T + Qlo K^T (M128 N128 K64 twice) into one of
 //           two S buffers in TMEM, O += P V (M128 N64 K128) into the O accumulator in TMEM, and
 //           L += P 1 (M128 N16 K128, B = a tile of ones) so that each row's softmax denominator
-//           is summed by the tensor core from exactly the weights the P V product uses;
+//           is summed by the tensor core from exactly the weights the P V product uses; the
+//           scores of tile g+1 are always issued before the P V product of tile g;
 //   warps 2-9  softmax: two threads per query row, each owning 64 of the tile's 128 keys.  A
 //           thread reads its half of the S row from TMEM, masks edge tiles, shares the row
 //           maximum with its partner through shared memory, writes P = exp2(s - m) as bf16
 //           into shared memory in the swizzled K-major layout the P V product reads, and
 //           rescales its half of the O row (and the L column) in TMEM when the maximum moved
-//           by more than 2^8; at the end it folds the sink in, normalises and stores 64 bytes
-//           of bf16 output.  Two softmax warps per scheduler hide each other's TMEM and MUFU
-//           latencies; with the sums on the tensor core a key costs one FMA, one exp2 and half
-//           a convert per thread.
-// S is double-buffered so that S(j+1) = Q K(j+1)^T is computed while the softmax of tile j runs.
+//           by more than 2^8; at the end of an item it folds the sink in, normalises and stores
+//           64 bytes of bf16 output.
 // Tiles entirely outside a query tile's causal / window range are never visited (the loop
 // bounds exclude them, as kernels.metal:631-634 does); only edge tiles are masked per element.
 //
@@ -39,53 +41,80 @@ namespace cc {
 namespace {
 
 constexpr int kTileQ = 128, kTileK = 128;
-constexpr int kStagesKV = 3;
+constexpr int kStagesK = 2, kStagesV = 3;
 constexpr int kThreadsPrefill = 320;
 constexpr int kSoftmaxThreads = 256;
 constexpr int kPlaneBytes = kTileQ * kHeadDim * 2;          // 16 KiB: 128 rows of 128 bytes
-constexpr int kOffQhi = 0;
-constexpr int kOffQlo = kPlaneBytes;
-constexpr int kOffK = 2 * kPlaneBytes;
-constexpr int kOffV = kOffK + kStagesKV * kPlaneBytes;
-constexpr int kOffP = kOffV + kStagesKV * kPlaneBytes;      // 2 buffers of 128 x 128 bf16
+constexpr int kOffQ = 0;                                    // 2 buffers of (hi plane, lo plane)
+constexpr int kOffK = 2 * 2 * kPlaneBytes;
+constexpr int kOffV = kOffK + kStagesK * kPlaneBytes;
+constexpr int kOffP = kOffV + kStagesV * kPlaneBytes;       // 2 buffers of 128 x 128 bf16
 constexpr int kOffOnes = kOffP + 2 * 2 * kPlaneBytes;       // 16 rows x 128 bytes of bf16 1.0
 constexpr int kOffXchg = kOffOnes + 2048;                   // [2 tiles in flight][2 halves][128 rows] f32
 constexpr int kOffBars = kOffXchg + 2 * 2 * 128 * 4;
-constexpr int kPrefillSmem = kOffBars + 256 + 1024;
+constexpr int kSeqCache = 512;                              // sequences whose offsets are kept in shared memory
+constexpr int kOffSeq = kOffBars + 256;                     // q_offsets[0..n] then starts[0..n-1]
+constexpr int kPrefillSmem = kOffSeq + (2 * kSeqCache + 1) * 4 + 1024;
 constexpr uint32_t kTmemCols = 512;                         // S0 0-127, S1 128-255, O 256-319, L 320-335
 constexpr uint32_t kColO = 256;
 constexpr uint32_t kColL = 320;
 constexpr float kRescaleThreshold = 8.0f;                   // log2 domain
 
 struct Bars {
-    uint64_t q_full;
-    uint64_t k_full[kStagesKV], k_empty[kStagesKV], v_full[kStagesKV], v_empty[kStagesKV];
+    uint64_t q_full[2], q_empty[2];
+    uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
     uint64_t s_full[2], p_full[2], pv_done[2];
+    uint64_t o_free;
     uint32_t tmem_base;
     uint32_t pad;
 };
+static_assert(sizeof(Bars) <= 256, "barrier block");
 
 __device__ __forceinline__ float neg_inf_f() { return __int_as_float(0xff800000); }
 
+// One work item: 128 queries (fewer at a sequence's end) of one head.
+struct Item {
+    bool valid;
+    int head, kv_head, seq;
+    int row0;        // first row of the sequence in q / out
+    int t;           // new positions of the sequence
+    int q0;          // first query of this tile within them
+    int end;         // start + t: keys beyond are not there
+    int first_pos, last_pos;
+    int kt_lo, n_tiles;
+};
+
+// `q_offsets` and `starts` point at the shared-memory copies when the sequences fit there: item
+// boundaries sit on the tensor-core thread's critical path and must not wait on global loads.
+__device__ __forceinline__ Item make_item(const PrefillParams &p, const int32_t *q_offsets, const int32_t *starts,
+                                          int id, int n_qt) {
+    Item it;
+    it.head = id % static_cast<int>(p.heads);
+    const int r = id / static_cast<int>(p.heads);
+    const int q_tile = n_qt - 1 - (r % n_qt);   // long tiles first
+    it.seq = r / n_qt;
+    it.kv_head = it.head / kGroup;
+    it.row0 = q_offsets[it.seq];
+    it.t = q_offsets[it.seq + 1] - it.row0;
+    it.q0 = q_tile * kTileQ;
+    it.valid = it.q0 < it.t;
+    const int start = starts[it.seq];
+    it.end = start + it.t;
+    it.first_pos = start + it.q0;
+    it.last_pos = start + min(it.q0 + kTileQ, it.t) - 1;
+    const int W = static_cast<int>(p.window);
+    const int key_lo = (W != 0 && it.first_pos + 1 > W) ? it.first_pos + 1 - W : 0;
+    it.kt_lo = key_lo / kTileK;
+    it.n_tiles = it.valid ? it.last_pos / kTileK - it.kt_lo + 1 : 0;
+    return it;
+}
+
 __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __grid_constant__ PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    const int head = blockIdx.x;
-    const int seq = blockIdx.z;
-    const int q_tile = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);  // long tiles first
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-    const int row0 = p.q_offsets[seq];
-    const int t = p.q_offsets[seq + 1] - row0;
-    const int q0 = q_tile * kTileQ;
-    if (q0 >= t) return;
-    const int start = p.starts[seq];
-    const int end = start + t;
-    const int first_pos = start + q0;
-    const int last_pos = start + min(q0 + kTileQ, t) - 1;
+    const int n_qt = (static_cast<int>(p.max_t) + kTileQ - 1) / kTileQ;
+    const int n_items = static_cast<int>(p.seqs) * n_qt * static_cast<int>(p.heads);
     const int W = static_cast<int>(p.window);
-    const int key_lo = (W != 0 && first_pos + 1 > W) ? first_pos + 1 - W : 0;
-    const int kt_lo = key_lo / kTileK, kt_hi = last_pos / kTileK;
-    const int n_tiles = kt_hi - kt_lo + 1;
 
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -93,24 +122,36 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
     const uint32_t smem_base = smem_u32(smem);
 
     if (warp == 0 && lane == 0) {
-        mbar_init(&bars->q_full, 1);
-        for (int s = 0; s < kStagesKV; ++s) {
-            mbar_init(&bars->k_full[s], 1);
-            mbar_init(&bars->k_empty[s], 1);
-            mbar_init(&bars->v_full[s], 1);
-            mbar_init(&bars->v_empty[s], 1);
-        }
         for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->q_full[b], 1);
+            mbar_init(&bars->q_empty[b], 1);
             mbar_init(&bars->s_full[b], 1);
             mbar_init(&bars->p_full[b], kSoftmaxThreads);
             mbar_init(&bars->pv_done[b], 1);
         }
+        for (int s = 0; s < kStagesK; ++s) {
+            mbar_init(&bars->k_full[s], 1);
+            mbar_init(&bars->k_empty[s], 1);
+        }
+        for (int s = 0; s < kStagesV; ++s) {
+            mbar_init(&bars->v_full[s], 1);
+            mbar_init(&bars->v_empty[s], 1);
+        }
+        mbar_init(&bars->o_free, kSoftmaxThreads);
         mbar_fence_init();
         fence_proxy_async();
     }
     if (warp == 1) {
         tmem_alloc(&bars->tmem_base, kTmemCols);
         tmem_relinquish();
+    }
+    const int32_t *q_offsets = p.q_offsets, *starts = p.starts;
+    if (p.seqs <= kSeqCache) {
+        int32_t *cache = reinterpret_cast<int32_t *>(smem + kOffSeq);
+        for (int i = tid; i <= static_cast<int>(p.seqs); i += kThreadsPrefill) cache[i] = p.q_offsets[i];
+        for (int i = tid; i < static_cast<int>(p.seqs); i += kThreadsPrefill) cache[p.seqs + 1 + i] = p.starts[i];
+        q_offsets = cache;
+        starts = cache + p.seqs + 1;
     }
     // the ones tile: any arrangement of ones is the same tile, so the swizzle does not matter
     for (int i = tid; i < 2048 / 4; i += kThreadsPrefill) reinterpret_cast<uint32_t *>(smem + kOffOnes)[i] = 0x3f803f80u;
@@ -120,55 +161,61 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
 
-    const int kv_head = head / kGroup;
-
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
-        // Lanes 0-7 each bring one 16-key page of K per tile, lanes 8-15 the same page of V: the
-        // sixteen block-table look-ups and TMA issues of a tile go out side by side instead of
-        // one after the other from a single thread.
-        if (lane == 0) {
-            mbar_expect_tx(&bars->q_full, 2 * kPlaneBytes);
-            tma_load_3d(smem + kOffQhi, &p.q_hi_map, 0, head, row0 + q0, &bars->q_full);
-            tma_load_3d(smem + kOffQlo, &p.q_lo_map, 0, head, row0 + q0, &bars->q_full);
-        }
-        const int32_t *table_row = p.block_table + static_cast<size_t>(seq) * p.max_pages;
         const int pg = lane & 7;
         const bool is_v = lane >= 8;
-        // row of this lane's page in the pool (a row past the end of the tensor = TMA writes zeros)
-        auto lookup = [&](int kt) -> int {
-            const int lp = kt * 8 + pg;
-            int y = static_cast<int>(p.pool_rows);
-            if (lane < 16 && lp * kPageTokens < end) {
-                uint32_t idx = static_cast<uint32_t>(lp);
-                if (p.ring_pages) idx %= p.ring_pages;
-                const int32_t page = idx < p.max_pages ? table_row[idx] : -1;
-                if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages)
-                    raise_status(p.status, kStatusBadPage);
-                else
-                    y = (page * static_cast<int>(p.kv_heads) + kv_head) * kTileRows + (is_v ? kPageTokens : 0);
-            }
-            return y;
-        };
         bool ok = true;
-        int y_next = lookup(kt_lo);
-        for (int j = 0; j < n_tiles; ++j) {
-            const int stage = j % kStagesKV;
-            const int y = y_next;
-            if (j + 1 < n_tiles) y_next = lookup(kt_lo + j + 1);   // in flight while this tile is issued
+        int n_it = 0, g = 0;
+        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
+            const Item it = make_item(p, q_offsets, starts, id, n_qt);
+            if (!it.valid) continue;
+            const int qb = n_it & 1;
             if (lane == 0) {
-                if (j >= kStagesKV) ok = mbar_wait(&bars->k_empty[stage], ((j / kStagesKV) - 1) & 1);
-                if (ok) mbar_expect_tx(&bars->k_full[stage], kPlaneBytes);
-            } else if (lane == 8) {
-                if (j >= kStagesKV) ok = mbar_wait(&bars->v_empty[stage], ((j / kStagesKV) - 1) & 1);
-                if (ok) mbar_expect_tx(&bars->v_full[stage], kPlaneBytes);
+                if (n_it >= 2) ok = mbar_wait(&bars->q_empty[qb], ((n_it >> 1) - 1) & 1);
+                if (ok) {
+                    uint8_t *q_dst = smem + kOffQ + qb * 2 * kPlaneBytes;
+                    mbar_expect_tx(&bars->q_full[qb], 2 * kPlaneBytes);
+                    tma_load_3d(q_dst, &p.q_hi_map, 0, it.head, it.row0 + it.q0, &bars->q_full[qb]);
+                    tma_load_3d(q_dst + kPlaneBytes, &p.q_lo_map, 0, it.head, it.row0 + it.q0, &bars->q_full[qb]);
+                }
             }
-            ok = __all_sync(0xffffffffu, ok);   // also orders the expect_tx before the loads below
-            if (!ok) break;
-            if (lane < 8)
-                tma_load_2d(smem + kOffK + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->k_full[stage]);
-            else if (lane < 16)
-                tma_load_2d(smem + kOffV + stage * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->v_full[stage]);
+            const int32_t *table_row = p.block_table + static_cast<size_t>(it.seq) * p.max_pages;
+            // row of this lane's page in the pool (a row past the end of the tensor = TMA writes zeros)
+            auto lookup = [&](int kt) -> int {
+                const int lp = kt * 8 + pg;
+                int y = static_cast<int>(p.pool_rows);
+                if (lane < 16 && lp * kPageTokens < it.end) {
+                    uint32_t idx = static_cast<uint32_t>(lp);
+                    if (p.ring_pages) idx %= p.ring_pages;
+                    const int32_t page = idx < p.max_pages ? table_row[idx] : -1;
+                    if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages)
+                        raise_status(p.status, kStatusBadPage);
+                    else
+                        y = (page * static_cast<int>(p.kv_heads) + it.kv_head) * kTileRows + (is_v ? kPageTokens : 0);
+                }
+                return y;
+            };
+            int y_next = lookup(it.kt_lo);
+            for (int j = 0; j < it.n_tiles; ++j, ++g) {
+                const int sk = g % kStagesK, sv = g % kStagesV;
+                const int y = y_next;
+                if (j + 1 < it.n_tiles) y_next = lookup(it.kt_lo + j + 1);   // in flight while this tile is issued
+                if (lane == 0) {
+                    if (g >= kStagesK) ok = ok && mbar_wait(&bars->k_empty[sk], ((g / kStagesK) - 1) & 1);
+                    if (ok) mbar_expect_tx(&bars->k_full[sk], kPlaneBytes);
+                } else if (lane == 8) {
+                    if (g >= kStagesV) ok = mbar_wait(&bars->v_empty[sv], ((g / kStagesV) - 1) & 1);
+                    if (ok) mbar_expect_tx(&bars->v_full[sv], kPlaneBytes);
+                }
+                ok = __all_sync(0xffffffffu, ok);   // also orders the expect_tx before the loads below
+                if (!ok) break;
+                if (lane < 8)
+                    tma_load_2d(smem + kOffK + sk * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->k_full[sk]);
+                else if (lane < 16)
+                    tma_load_2d(smem + kOffV + sv * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->v_full[sv]);
+            }
+            ++n_it;
         }
         if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
         __syncwarp();
@@ -179,45 +226,80 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
             constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true);
             constexpr uint32_t idesc_l = umma_idesc_bf16(kTileQ, 16, false);
             const uint64_t ones_desc = smem_desc_sw128(smem_base + kOffOnes, 16, 1024);
-            const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQhi, 16, 1024);
-            const uint64_t qlo_desc = smem_desc_sw128(smem_base + kOffQlo, 16, 1024);
-            bool ok = mbar_wait(&bars->q_full, 0);
-            tc_fence_after();
-            auto issue_qk = [&](int j) -> bool {
-                const int stage = j % kStagesKV;
-                if (!mbar_wait(&bars->k_full[stage], (j / kStagesKV) & 1)) return false;
+            bool ok = true;
+            // Two cursors over the same item sequence: the score cursor runs one tile ahead of
+            // the product cursor, across item boundaries.
+            struct Cursor {
+                int id, n_it, j, g;
+                Item it;
+            };
+            auto advance_item = [&](Cursor &c) {   // moves to the next valid item (or past the end)
+                while (c.id < n_items) {
+                    c.it = make_item(p, q_offsets, starts, c.id, n_qt);
+                    if (c.it.valid) return;
+                    c.id += gridDim.x;
+                }
+            };
+            auto step = [&](Cursor &c) {           // next tile
+                ++c.g;
+                if (++c.j == c.it.n_tiles) {
+                    c.j = 0;
+                    ++c.n_it;
+                    c.id += gridDim.x;
+                    advance_item(c);
+                }
+            };
+            Cursor qk{static_cast<int>(blockIdx.x), 0, 0, 0, {}}, pv{static_cast<int>(blockIdx.x), 0, 0, 0, {}};
+            advance_item(qk);
+            advance_item(pv);
+            auto issue_qk = [&](Cursor &c) -> bool {
+                const int qb = c.n_it & 1, sk = c.g % kStagesK;
+                if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.n_it >> 1) & 1)) return false;
+                if (!mbar_wait(&bars->k_full[sk], (c.g / kStagesK) & 1)) return false;
                 tc_fence_after();
-                const uint64_t k_desc = smem_desc_sw128(smem_base + kOffK + stage * kPlaneBytes, 16, 1024);
-                const uint32_t d = tmem + static_cast<uint32_t>(j & 1) * kTileK;
+                const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + qb * 2 * kPlaneBytes, 16, 1024);
+                const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
+                const uint64_t k_desc = smem_desc_sw128(smem_base + kOffK + sk * kPlaneBytes, 16, 1024);
+                const uint32_t d = tmem + static_cast<uint32_t>(c.g & 1) * kTileK;
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qhi_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qlo_desc + ks * 2, k_desc + ks * 2, idesc_qk, true);
-                umma_commit(&bars->s_full[j & 1]);
-                umma_commit(&bars->k_empty[stage]);
+                umma_commit(&bars->s_full[c.g & 1]);
+                umma_commit(&bars->k_empty[sk]);
+                if (c.j == c.it.n_tiles - 1) umma_commit(&bars->q_empty[qb]);   // last scores of this item
                 return true;
             };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-                if (!ok) break;
-                const int stage = j % kStagesKV;
-                ok = mbar_wait(&bars->p_full[j & 1], (j >> 1) & 1);
-                if (ok) ok = mbar_wait(&bars->v_full[stage], (j / kStagesKV) & 1);
+            if (qk.id < n_items) {
+                ok = issue_qk(qk);
+                step(qk);
+            }
+            while (ok && pv.id < n_items) {
+                if (qk.id < n_items) {
+                    ok = issue_qk(qk);
+                    step(qk);
+                    if (!ok) break;
+                }
+                const int b = pv.g & 1, sv = pv.g % kStagesV;
+                // the first product of an item overwrites O and L: the previous item's rows must be out
+                if (pv.j == 0 && pv.n_it > 0) ok = mbar_wait(&bars->o_free, (pv.n_it - 1) & 1);
+                if (ok) ok = mbar_wait(&bars->p_full[b], (pv.g >> 1) & 1);
+                if (ok) ok = mbar_wait(&bars->v_full[sv], (pv.g / kStagesV) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t p_desc = smem_desc_sw128(smem_base + kOffP + (j & 1) * 2 * kPlaneBytes, 16, 1024);
-                const uint64_t v_desc = smem_desc_sw128(smem_base + kOffV + stage * kPlaneBytes, 1024, 1024);
+                const uint64_t p_desc = smem_desc_sw128(smem_base + kOffP + b * 2 * kPlaneBytes, 16, 1024);
+                const uint64_t v_desc = smem_desc_sw128(smem_base + kOffV + sv * kPlaneBytes, 1024, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     umma_bf16(tmem + kColO, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2,
-                              v_desc + ks * (2048 >> 4), idesc_pv, j > 0 || ks > 0);
+                              v_desc + ks * (2048 >> 4), idesc_pv, pv.j > 0 || ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     umma_bf16(tmem + kColL, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2, ones_desc, idesc_l,
-                              j > 0 || ks > 0);
-                umma_commit(&bars->pv_done[j & 1]);
-                umma_commit(&bars->v_empty[stage]);
+                              pv.j > 0 || ks > 0);
+                umma_commit(&bars->pv_done[b]);
+                umma_commit(&bars->v_empty[sv]);
+                step(pv);
             }
             if (!ok) raise_status(p.status, kStatusWaitTimeout);
         }
@@ -227,60 +309,63 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         const int quarter = warp & 3;                 // the TMEM lanes this warp can reach
         const int half = (warp - 2) >> 2;             // which 64 of the tile's 128 keys, which 32 of O's 64 columns
         const int row = quarter * 32 + lane;          // row of the query tile
-        const int pos = first_pos + row;              // absolute position of this query
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        const int vis_lo = (W != 0 && pos + 1 > W) ? pos + 1 - W : 0;
         float *xchg = reinterpret_cast<float *>(smem + kOffXchg);
-        float m = neg_inf_f();
-        bool ok = true;
         uint8_t *p_row_base = smem + kOffP + half * kPlaneBytes + row * 128;
         const int sw = row & 7;
         const float scale = p.scale_log2e;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            ok = mbar_wait(&bars->s_full[b], (j >> 1) & 1);
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t s[2][32];
+        bool ok = true;
+        int n_it = 0, g = 0;
+        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
+            const Item it = make_item(p, q_offsets, starts, id, n_qt);
+            if (!it.valid) continue;
+            const int pos = it.first_pos + row;       // absolute position of this query
+            const int vis_lo = (W != 0 && pos + 1 > W) ? pos + 1 - W : 0;
+            float m = neg_inf_f();
+            for (int j = 0; j < it.n_tiles; ++j, ++g) {
+                const int b = g & 1;
+                ok = mbar_wait(&bars->s_full[b], (g >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t s[2][32];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tmem_ld_x32(tmem + lane_addr + b * kTileK + half * 64 + c * 32, s[c]);
-            tmem_wait_ld();
-            const int kt = kt_lo + j;
-            const int key0 = kt * kTileK + half * 64;
-            const bool edge = (kt * kTileK + kTileK - 1 > first_pos) || (W != 0 && kt * kTileK + W <= last_pos);
-            if (edge) {
+                for (int c = 0; c < 2; ++c) tmem_ld_x32(tmem + lane_addr + b * kTileK + half * 64 + c * 32, s[c]);
+                tmem_wait_ld();
+                const int kt = it.kt_lo + j;
+                const int key0 = kt * kTileK + half * 64;
+                const bool edge = (kt * kTileK + kTileK - 1 > it.first_pos) || (W != 0 && kt * kTileK + W <= it.last_pos);
+                if (edge) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int key = key0 + c * 32 + i;
+                            if (key > pos || key < vis_lo) s[c][i] = 0xff800000u;
+                        }
+                }
+                float mx = neg_inf_f();
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = key0 + c * 32 + i;
-                        if (key > pos || key < vis_lo) s[c][i] = 0xff800000u;
-                    }
-            }
-            float mx = neg_inf_f();
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; i += 2)
-                    mx = fmaxf(mx, fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
-            // the row maximum over both halves: through shared memory, one named barrier per tile
-            xchg[(b * 2 + half) * 128 + row] = mx;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            mx = fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * 128 + row]);
-            const float m_cand = fmaxf(m, mx * scale);
-            // keep the old maximum unless it moved by more than 2^8: fewer trips through TMEM
-            const bool move = (m_cand > m + kRescaleThreshold) || (m == neg_inf_f() && m_cand > m);
-            const float m_new = move ? m_cand : m;
-            const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
-            const float alpha = move ? ex2(m - m_use) : 1.0f;
-            m = m_new;
-            // Only a rescale has to wait for the previous tile's P V product; the common case goes
-            // straight on to its exponentials while that product is still running.
-            if (j > 0 && __any_sync(0xffffffffu, move)) {
-                ok = mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1);
-                if (!ok) break;
-                tc_fence_after();
-                {
+                    for (int i = 0; i < 32; i += 2)
+                        mx = fmaxf(mx, fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
+                // the row maximum over both halves: through shared memory, one named barrier per tile
+                xchg[(b * 2 + half) * 128 + row] = mx;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                mx = fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * 128 + row]);
+                const float m_cand = fmaxf(m, mx * scale);
+                // keep the old maximum unless it moved by more than 2^8: fewer trips through TMEM
+                const bool move = (m_cand > m + kRescaleThreshold) || (m == neg_inf_f() && m_cand > m);
+                const float m_new = move ? m_cand : m;
+                const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
+                const float alpha = move ? ex2(m - m_use) : 1.0f;
+                m = m_new;
+                // Only a rescale has to wait for the previous tile's P V product; the common case
+                // goes straight on to its exponentials while that product is still running.
+                if (j > 0 && __any_sync(0xffffffffu, move)) {
+                    ok = mbar_wait(&bars->pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
                     uint32_t o[32];
                     tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
                     tmem_wait_ld();
@@ -296,54 +381,55 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                     }
                     tmem_wait_st();
                 }
-            }
-            // the P buffer of this parity was last read by the product of tile j - 2
-            if (j >= 2) {
-                ok = mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1);
-                if (!ok) break;
-            }
-            // P = exp2(s * scale - m) as bf16, 8 keys (16 bytes) at a time, into the swizzled tile
-            uint8_t *p_row = p_row_base + b * 2 * kPlaneBytes;
-            const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 x = ffma2(make_float2(__uint_as_float(s[c][q8 * 8 + 2 * e]),
-                                                           __uint_as_float(s[c][q8 * 8 + 2 * e + 1])),
-                                               scale2, neg_m2);
-                        w[e] = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
-                    }
-                    const int chunk = c * 4 + q8;           // 8 chunks of 8 keys in this thread's half
-                    *reinterpret_cast<uint4 *>(p_row + ((chunk ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                // the P buffer of this parity was last read by the product of tile g - 2
+                if (g >= 2) {
+                    ok = mbar_wait(&bars->pv_done[b], ((g - 2) >> 1) & 1);
+                    if (!ok) break;
                 }
+                // P = exp2(s * scale - m) as bf16, 8 keys (16 bytes) at a time, into the swizzled tile
+                uint8_t *p_row = p_row_base + b * 2 * kPlaneBytes;
+                const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 x = ffma2(make_float2(__uint_as_float(s[c][q8 * 8 + 2 * e]),
+                                                               __uint_as_float(s[c][q8 * 8 + 2 * e + 1])),
+                                                   scale2, neg_m2);
+                            w[e] = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
+                        }
+                        const int chunk = c * 4 + q8;           // 8 chunks of 8 keys in this thread's half
+                        *reinterpret_cast<uint4 *>(p_row + ((chunk ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+                fence_proxy_async();      // make the P stores visible to the tensor core's reads
+                tc_fence_before();
+                mbar_arrive(&bars->p_full[b]);
             }
-            fence_proxy_async();      // make the P stores visible to the tensor core's reads
-            tc_fence_before();
-            mbar_arrive(&bars->p_full[b]);
-        }
-        if (ok) {
-            ok = mbar_wait(&bars->pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
-        }
-        if (ok) {
+            if (!ok) break;
+            // ---- the item's rows: wait for its last product, read O and L, hand them back, store
+            ok = mbar_wait(&bars->pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1);
+            if (!ok) break;
             tc_fence_after();
             uint32_t lsum;
             tmem_ld_x1(tmem + lane_addr + kColL, lsum);
             uint32_t o[32];
             tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&bars->o_free);    // the next item's first product may overwrite O and L now
             const float l = __uint_as_float(lsum);
-            const float sink2 = p.sinks ? p.sinks[head] * 1.4426950408889634f : neg_inf_f();
+            const float sink2 = p.sinks ? p.sinks[it.head] * 1.4426950408889634f : neg_inf_f();
             const float Mt = fmaxf(m, sink2);
             const float e = m == neg_inf_f() ? 0.f : ex2(m - Mt);
             const float total = l * e + (p.sinks ? ex2(sink2 - Mt) : 0.f);
             const float inv = total > 0.f ? e / total : 0.f;
-            if (q0 + row < t) {
+            if (it.q0 + row < it.t) {
                 uint16_t *out_row =
-                    p.out + (static_cast<size_t>(row0 + q0 + row) * p.heads + head) * kHeadDim + half * 32;
+                    p.out + (static_cast<size_t>(it.row0 + it.q0 + row) * p.heads + it.head) * kHeadDim + half * 32;
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint4 v = make_uint4(pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
@@ -353,9 +439,9 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                     *reinterpret_cast<uint4 *>(out_row + i) = v;
                 }
             }
-        } else {
-            if (lane == 0) raise_status(p.status, kStatusWaitTimeout);
+            ++n_it;
         }
+        if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
     }
     tc_fence_before();
     __syncthreads();
@@ -369,7 +455,11 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
 
 void launch_prefill(const PrefillParams &p, cudaStream_t stream) {
     cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
-    dim3 grid(p.heads, (p.max_t + kTileQ - 1) / kTileQ, p.seqs);
+    int device = 0, sms = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long long items = static_cast<long long>(p.seqs) * ((p.max_t + kTileQ - 1) / kTileQ) * p.heads;
+    const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);   // one persistent CTA per SM
     prefill_kernel<<<grid, kThreadsPrefill, kPrefillSmem, stream>>>(p);
 }
 
