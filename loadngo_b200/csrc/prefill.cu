@@ -12,20 +12,23 @@
 // fixed sequence of items (heaviest first, the 8 heads of a KV group next to each other so that
 // they share K and V through L2), and its pipelines run on across item boundaries: while the
 // softmax warps finish one item, the producer is already loading the next item's Q, K and V and
-// the tensor core is already computing its first scores.  Ten warps, three roles:
+// the tensor core is already computing its first scores.  Eleven warps, four roles:
 //   warp 0  producer: TMA loads of the Q tile (hi and lo planes, double-buffered) and, per
 //           128-key tile, eight 16-key pages of K and of V, found through the block table, into
 //           rings (sixteen lanes look up and issue one page each);
-//   warp 1  one thread issues tcgen05.mma: S = Qhi K^T + Qlo K^T (M128 N128 K64 twice) into one of
-//           two S buffers in TMEM, O += P V (M128 N64 K128) into the O accumulator in TMEM, and
-//           L += P 1 (M128 N16 K128, B = a tile of ones) so that each row's softmax denominator
-//           is summed by the tensor core from exactly the weights the P V product uses; the
-//           scores of tile g+1 are always issued before the P V product of tile g;
+//   warp 1  one thread issues the score products S = Qhi K^T + Qlo K^T (tcgen05.mma M128 N128 K64
+//           twice) into one of two S buffers in TMEM, up to two tiles ahead of the products;
+//   warp 10 one thread issues O += P V (M128 N64 K128, P read from TMEM) into the O accumulator
+//           in TMEM.  Every tcgen05.mma costs about 60 cycles of tensor pipe however narrow it is
+//           (measured), so nothing small rides on the tensor core (the row sums stay with the
+//           softmax threads), and the two streams have an issuer each so that one thread's
+//           barrier traffic never leaves the pipe empty;
 //   warps 2-9  softmax: two threads per query row, each owning 64 of the tile's 128 keys.  A
 //           thread reads its half of the S row from TMEM, masks edge tiles, shares the row
 //           maximum with its partner through shared memory, writes P = exp2(s - m) as bf16
-//           into shared memory in the swizzled K-major layout the P V product reads, and
-//           rescales its half of the O row (and the L column) in TMEM when the maximum moved
+//           back into tensor memory over the scores it came from (the products read their A
+//           operand from TMEM, so P never touches shared memory, whose bandwidth the Q K^T
+//           operands already use), and rescales its half of the O row (and the L column) in TMEM when the maximum moved
 //           by more than 2^8; at the end of an item it folds the sink in, normalises and stores
 //           64 bytes of bf16 output.
 // Tiles entirely outside a query tile's causal / window range are never visited (the loop
@@ -41,29 +44,29 @@ namespace cc {
 namespace {
 
 constexpr int kTileQ = 128, kTileK = 128;
-constexpr int kStagesK = 2, kStagesV = 3;
-constexpr int kThreadsPrefill = 320;
+constexpr int kStagesKV = 3;                               // K tile + V tile per stage
+constexpr int kPvRing = 6;                                  // "product done" barriers, by tile index mod 6
+constexpr int kThreadsPrefill = 352;
 constexpr int kSoftmaxThreads = 256;
 constexpr int kPlaneBytes = kTileQ * kHeadDim * 2;          // 16 KiB: 128 rows of 128 bytes
 constexpr int kOffQ = 0;                                    // 2 buffers of (hi plane, lo plane)
-constexpr int kOffK = 2 * 2 * kPlaneBytes;
-constexpr int kOffV = kOffK + kStagesK * kPlaneBytes;
-constexpr int kOffP = kOffV + kStagesV * kPlaneBytes;       // 2 buffers of 128 x 128 bf16
-constexpr int kOffOnes = kOffP + 2 * 2 * kPlaneBytes;       // 16 rows x 128 bytes of bf16 1.0
-constexpr int kOffXchg = kOffOnes + 2048;                   // [2 tiles in flight][2 halves][128 rows] f32
-constexpr int kOffBars = kOffXchg + 2 * 2 * 128 * 4;
+constexpr int kOffKV = 2 * 2 * kPlaneBytes;                 // per stage: K tile then V tile
+constexpr int kOffXchg = kOffKV + kStagesKV * 2 * kPlaneBytes;    // [2 tiles in flight + 1 for row sums][2 halves][128 rows] f32
+constexpr int kOffBars = kOffXchg + 3 * 2 * 128 * 4;
 constexpr int kSeqCache = 512;                              // sequences whose offsets are kept in shared memory
 constexpr int kOffSeq = kOffBars + 256;                     // q_offsets[0..n] then starts[0..n-1]
 constexpr int kPrefillSmem = kOffSeq + (2 * kSeqCache + 1) * 4 + 1024;
-constexpr uint32_t kTmemCols = 512;                         // S0 0-127, S1 128-255, O 256-319, L 320-335
+// TMEM columns: S0 0-127, S1 128-255 (P(g) overwrites the first 64 columns of S(g)'s buffer as
+// packed bf16 pairs once both threads of every row hold their scores in registers), O 256-319.
+constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 256;
-constexpr uint32_t kColL = 320;
 constexpr float kRescaleThreshold = 8.0f;                   // log2 domain
 
 struct Bars {
     uint64_t q_full[2], q_empty[2];
-    uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
-    uint64_t s_full[2], p_full[2], pv_done[2];
+    uint64_t kv_full[kStagesKV];
+    uint64_t s_full[2], p_full[2];
+    uint64_t pv_done[kPvRing];   // tile g's product: frees its K/V stage, its P columns, and O for a rescale
     uint64_t o_free;
     uint32_t tmem_base;
     uint32_t pad;
@@ -71,6 +74,23 @@ struct Bars {
 static_assert(sizeof(Bars) <= 256, "barrier block");
 
 __device__ __forceinline__ float neg_inf_f() { return __int_as_float(0xff800000); }
+
+// Optional cycle accounting of where each role waits (built only with -DCC_PREFILL_PROF).
+#ifdef CC_PREFILL_PROF
+__device__ unsigned long long g_prefill_prof[16];
+#define PROF_T0() const long long prof_t0_ = clock64()
+#define PROF_ADD(slot) atomicAdd(&g_prefill_prof[slot], static_cast<unsigned long long>(clock64() - prof_t0_))
+#define PROF_WAIT(slot, expr) [&] { const long long t_ = clock64(); const bool r_ = (expr); \
+    atomicAdd(&g_prefill_prof[slot], static_cast<unsigned long long>(clock64() - t_)); return r_; }()
+#define PROF_BEGIN(name) const long long name = clock64()
+#define PROF_END(slot, name) atomicAdd(&g_prefill_prof[slot], static_cast<unsigned long long>(clock64() - name))
+#else
+#define PROF_BEGIN(name)
+#define PROF_END(slot, name)
+#define PROF_T0()
+#define PROF_ADD(slot)
+#define PROF_WAIT(slot, expr) (expr)
+#endif
 
 // One work item: 128 queries (fewer at a sequence's end) of one head.
 struct Item {
@@ -127,16 +147,9 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
             mbar_init(&bars->q_empty[b], 1);
             mbar_init(&bars->s_full[b], 1);
             mbar_init(&bars->p_full[b], kSoftmaxThreads);
-            mbar_init(&bars->pv_done[b], 1);
         }
-        for (int s = 0; s < kStagesK; ++s) {
-            mbar_init(&bars->k_full[s], 1);
-            mbar_init(&bars->k_empty[s], 1);
-        }
-        for (int s = 0; s < kStagesV; ++s) {
-            mbar_init(&bars->v_full[s], 1);
-            mbar_init(&bars->v_empty[s], 1);
-        }
+        for (int s = 0; s < kStagesKV; ++s) mbar_init(&bars->kv_full[s], 1);
+        for (int s = 0; s < kPvRing; ++s) mbar_init(&bars->pv_done[s], 1);
         mbar_init(&bars->o_free, kSoftmaxThreads);
         mbar_fence_init();
         fence_proxy_async();
@@ -153,9 +166,6 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         q_offsets = cache;
         starts = cache + p.seqs + 1;
     }
-    // the ones tile: any arrangement of ones is the same tile, so the swizzle does not matter
-    for (int i = tid; i < 2048 / 4; i += kThreadsPrefill) reinterpret_cast<uint32_t *>(smem + kOffOnes)[i] = 0x3f803f80u;
-    fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -198,110 +208,84 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
             };
             int y_next = lookup(it.kt_lo);
             for (int j = 0; j < it.n_tiles; ++j, ++g) {
-                const int sk = g % kStagesK, sv = g % kStagesV;
+                const int stage = g % kStagesKV;
                 const int y = y_next;
                 if (j + 1 < it.n_tiles) y_next = lookup(it.kt_lo + j + 1);   // in flight while this tile is issued
                 if (lane == 0) {
-                    if (g >= kStagesK) ok = ok && mbar_wait(&bars->k_empty[sk], ((g / kStagesK) - 1) & 1);
-                    if (ok) mbar_expect_tx(&bars->k_full[sk], kPlaneBytes);
-                } else if (lane == 8) {
-                    if (g >= kStagesV) ok = mbar_wait(&bars->v_empty[sv], ((g / kStagesV) - 1) & 1);
-                    if (ok) mbar_expect_tx(&bars->v_full[sv], kPlaneBytes);
+                    // the stage is free once the product of the tile that used it (g - 3) is done
+                    if (g >= kStagesKV)
+                        ok = PROF_WAIT(10, mbar_wait(&bars->pv_done[(g - kStagesKV) % kPvRing], ((g - kStagesKV) / kPvRing) & 1));
+                    if (ok) mbar_expect_tx(&bars->kv_full[stage], 2 * kPlaneBytes);
                 }
                 ok = __all_sync(0xffffffffu, ok);   // also orders the expect_tx before the loads below
                 if (!ok) break;
-                if (lane < 8)
-                    tma_load_2d(smem + kOffK + sk * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->k_full[sk]);
-                else if (lane < 16)
-                    tma_load_2d(smem + kOffV + sv * kPlaneBytes + pg * 2048, &p.pool_map, 0, y, &bars->v_full[sv]);
+                if (lane < 16)
+                    tma_load_2d(smem + kOffKV + stage * 2 * kPlaneBytes + (is_v ? kPlaneBytes : 0) + pg * 2048, &p.pool_map,
+                                0, y, &bars->kv_full[stage]);
             }
             ++n_it;
         }
         if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
         __syncwarp();
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || warp == 10) {
+        // ------------------------------------------- two MMA issuers: warp 1 scores, warp 10 products
+        // Each walks the CTA's item sequence on its own.  One thread issuing everything spent more
+        // time on barrier waits and commits between its instructions than the tensor pipe needs
+        // to run them; with two issuers the pipe always has the other stream's work queued.
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileQ, kTileK, false);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true);
-            constexpr uint32_t idesc_l = umma_idesc_bf16(kTileQ, 16, false);
-            const uint64_t ones_desc = smem_desc_sw128(smem_base + kOffOnes, 16, 1024);
+            const bool scores = warp == 1;
             bool ok = true;
-            // Two cursors over the same item sequence: the score cursor runs one tile ahead of
-            // the product cursor, across item boundaries.
-            struct Cursor {
-                int id, n_it, j, g;
-                Item it;
-            };
-            auto advance_item = [&](Cursor &c) {   // moves to the next valid item (or past the end)
-                while (c.id < n_items) {
-                    c.it = make_item(p, q_offsets, starts, c.id, n_qt);
-                    if (c.it.valid) return;
-                    c.id += gridDim.x;
+            int n_it = 0, g = 0;
+            PROF_T0();
+            for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
+                const Item it = make_item(p, q_offsets, starts, id, n_qt);
+                if (!it.valid) continue;
+                const int qb = n_it & 1;
+                if (scores) {
+                    ok = PROF_WAIT(0, mbar_wait(&bars->q_full[qb], (n_it >> 1) & 1));
+                    const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + qb * 2 * kPlaneBytes, 16, 1024);
+                    const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
+                    for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
+                        const int stage = g % kStagesKV;
+                        ok = PROF_WAIT(1, mbar_wait(&bars->kv_full[stage], (g / kStagesKV) & 1));
+                        // S(g) goes where P(g - 2) was: that product must have read it
+                        if (ok && g >= 2) ok = PROF_WAIT(2, mbar_wait(&bars->pv_done[(g - 2) % kPvRing], ((g - 2) / kPvRing) & 1));
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t k_desc = smem_desc_sw128(smem_base + kOffKV + stage * 2 * kPlaneBytes, 16, 1024);
+                        const uint32_t d = tmem + static_cast<uint32_t>(g & 1) * kTileK;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qhi_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks > 0);
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qlo_desc + ks * 2, k_desc + ks * 2, idesc_qk, true);
+                        umma_commit(&bars->s_full[g & 1]);
+                    }
+                    if (ok) umma_commit(&bars->q_empty[qb]);   // all scores of this item are issued
+                } else {
+                    // the first product of an item overwrites O: the previous item's rows must be out
+                    if (n_it > 0) ok = PROF_WAIT(3, mbar_wait(&bars->o_free, (n_it - 1) & 1));
+                    for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
+                        const int stage = g % kStagesKV, b = g & 1;
+                        ok = PROF_WAIT(4, mbar_wait(&bars->p_full[b], (g >> 1) & 1));
+                        if (ok) ok = mbar_wait(&bars->kv_full[stage], (g / kStagesKV) & 1);   // long since there
+                        if (!ok) break;
+                        tc_fence_after();
+                        // P comes from tensor memory: 16 keys of a k-step are 8 columns of packed bf16 pairs
+                        const uint32_t p_tmem = tmem + static_cast<uint32_t>(b) * kTileK;
+                        const uint64_t v_desc =
+                            smem_desc_sw128(smem_base + kOffKV + stage * 2 * kPlaneBytes + kPlaneBytes, 1024, 1024);
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks)
+                            umma_bf16_ts(tmem + kColO, p_tmem + ks * 8, v_desc + ks * (2048 >> 4), idesc_pv, j > 0 || ks > 0);
+                        umma_commit(&bars->pv_done[g % kPvRing]);
+                    }
                 }
-            };
-            auto step = [&](Cursor &c) {           // next tile
-                ++c.g;
-                if (++c.j == c.it.n_tiles) {
-                    c.j = 0;
-                    ++c.n_it;
-                    c.id += gridDim.x;
-                    advance_item(c);
-                }
-            };
-            Cursor qk{static_cast<int>(blockIdx.x), 0, 0, 0, {}}, pv{static_cast<int>(blockIdx.x), 0, 0, 0, {}};
-            advance_item(qk);
-            advance_item(pv);
-            auto issue_qk = [&](Cursor &c) -> bool {
-                const int qb = c.n_it & 1, sk = c.g % kStagesK;
-                if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.n_it >> 1) & 1)) return false;
-                if (!mbar_wait(&bars->k_full[sk], (c.g / kStagesK) & 1)) return false;
-                tc_fence_after();
-                const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + qb * 2 * kPlaneBytes, 16, 1024);
-                const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
-                const uint64_t k_desc = smem_desc_sw128(smem_base + kOffK + sk * kPlaneBytes, 16, 1024);
-                const uint32_t d = tmem + static_cast<uint32_t>(c.g & 1) * kTileK;
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qhi_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qlo_desc + ks * 2, k_desc + ks * 2, idesc_qk, true);
-                umma_commit(&bars->s_full[c.g & 1]);
-                umma_commit(&bars->k_empty[sk]);
-                if (c.j == c.it.n_tiles - 1) umma_commit(&bars->q_empty[qb]);   // last scores of this item
-                return true;
-            };
-            if (qk.id < n_items) {
-                ok = issue_qk(qk);
-                step(qk);
-            }
-            while (ok && pv.id < n_items) {
-                if (qk.id < n_items) {
-                    ok = issue_qk(qk);
-                    step(qk);
-                    if (!ok) break;
-                }
-                const int b = pv.g & 1, sv = pv.g % kStagesV;
-                // the first product of an item overwrites O and L: the previous item's rows must be out
-                if (pv.j == 0 && pv.n_it > 0) ok = mbar_wait(&bars->o_free, (pv.n_it - 1) & 1);
-                if (ok) ok = mbar_wait(&bars->p_full[b], (pv.g >> 1) & 1);
-                if (ok) ok = mbar_wait(&bars->v_full[sv], (pv.g / kStagesV) & 1);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t p_desc = smem_desc_sw128(smem_base + kOffP + b * 2 * kPlaneBytes, 16, 1024);
-                const uint64_t v_desc = smem_desc_sw128(smem_base + kOffV + sv * kPlaneBytes, 1024, 1024);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    umma_bf16(tmem + kColO, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2,
-                              v_desc + ks * (2048 >> 4), idesc_pv, pv.j > 0 || ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    umma_bf16(tmem + kColL, p_desc + (ks >> 2) * (kPlaneBytes >> 4) + (ks & 3) * 2, ones_desc, idesc_l,
-                              pv.j > 0 || ks > 0);
-                umma_commit(&bars->pv_done[b]);
-                umma_commit(&bars->v_empty[sv]);
-                step(pv);
+                ++n_it;
             }
             if (!ok) raise_status(p.status, kStatusWaitTimeout);
+            PROF_ADD(5);
         }
         __syncwarp();
     } else {
@@ -311,19 +295,24 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
         const int row = quarter * 32 + lane;          // row of the query tile
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         float *xchg = reinterpret_cast<float *>(smem + kOffXchg);
-        uint8_t *p_row_base = smem + kOffP + half * kPlaneBytes + row * 128;
-        const int sw = row & 7;
         const float scale = p.scale_log2e;
         bool ok = true;
         int n_it = 0, g = 0;
+#ifdef CC_PREFILL_PROF
+        const long long soft_t0 = clock64();
+#endif
         for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
             const Item it = make_item(p, q_offsets, starts, id, n_qt);
             if (!it.valid) continue;
             const int pos = it.first_pos + row;       // absolute position of this query
             const int vis_lo = (W != 0 && pos + 1 > W) ? pos + 1 - W : 0;
-            float m = neg_inf_f();
+            float m = neg_inf_f(), l = 0.f;   // l: this thread's half of the row sum
             for (int j = 0; j < it.n_tiles; ++j, ++g) {
                 const int b = g & 1;
+#ifdef CC_PREFILL_PROF
+                if (tid == 64) ok = PROF_WAIT(6, mbar_wait(&bars->s_full[b], (g >> 1) & 1));
+                else
+#endif
                 ok = mbar_wait(&bars->s_full[b], (g >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
@@ -360,10 +349,11 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                 const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
                 const float alpha = move ? ex2(m - m_use) : 1.0f;
                 m = m_new;
+                l *= alpha;
                 // Only a rescale has to wait for the previous tile's P V product; the common case
                 // goes straight on to its exponentials while that product is still running.
                 if (j > 0 && __any_sync(0xffffffffu, move)) {
-                    ok = mbar_wait(&bars->pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1);
+                    ok = mbar_wait(&bars->pv_done[(g - 1) % kPvRing], ((g - 1) / kPvRing) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     uint32_t o[32];
@@ -372,56 +362,50 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                     tmem_st_x32(tmem + lane_addr + kColO + half * 32, o);
-                    if (half == 0) {   // the row sum lives in column kColL; one of the two threads scales it
-                        uint32_t lsum;
-                        tmem_ld_x1(tmem + lane_addr + kColL, lsum);
-                        tmem_wait_ld();
-                        lsum = __float_as_uint(__uint_as_float(lsum) * alpha);
-                        tmem_st_x1(tmem + lane_addr + kColL, lsum);
-                    }
                     tmem_wait_st();
                 }
-                // the P buffer of this parity was last read by the product of tile g - 2
-                if (g >= 2) {
-                    ok = mbar_wait(&bars->pv_done[b], ((g - 2) >> 1) & 1);
-                    if (!ok) break;
-                }
-                // P = exp2(s * scale - m) as bf16, 8 keys (16 bytes) at a time, into the swizzled tile
-                uint8_t *p_row = p_row_base + b * 2 * kPlaneBytes;
+                // P = exp2(s * scale - m) as packed bf16 pairs, written over this row's scores in
+                // tensor memory (every thread of the CTA holds its scores in registers since the
+                // barrier above; the tensor core reads P before it overwrites the buffer again).
                 const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
+                uint32_t w[32];
+                float l_acc[2] = {0.f, 0.f};
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
 #pragma unroll
-                    for (int q8 = 0; q8 < 4; ++q8) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 x = ffma2(make_float2(__uint_as_float(s[c][q8 * 8 + 2 * e]),
-                                                               __uint_as_float(s[c][q8 * 8 + 2 * e + 1])),
-                                                   scale2, neg_m2);
-                            w[e] = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
-                        }
-                        const int chunk = c * 4 + q8;           // 8 chunks of 8 keys in this thread's half
-                        *reinterpret_cast<uint4 *>(p_row + ((chunk ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int e = 0; e < 16; ++e) {
+                        const float2 x = ffma2(make_float2(__uint_as_float(s[c][2 * e]), __uint_as_float(s[c][2 * e + 1])),
+                                               scale2, neg_m2);
+                        const uint32_t pair = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
+                        w[c * 16 + e] = pair;
+                        // the denominator sums the rounded weights, the ones the product uses
+                        l_acc[e & 1] += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
                     }
                 }
-                fence_proxy_async();      // make the P stores visible to the tensor core's reads
+                l += l_acc[0] + l_acc[1];
+                tmem_st_x32(tmem + lane_addr + b * kTileK + half * 32, w);
+                tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[b]);
             }
             if (!ok) break;
             // ---- the item's rows: wait for its last product, read O and L, hand them back, store
-            ok = mbar_wait(&bars->pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1);
+#ifdef CC_PREFILL_PROF
+            if (tid == 64) ok = PROF_WAIT(7, mbar_wait(&bars->pv_done[(g - 1) % kPvRing], ((g - 1) / kPvRing) & 1));
+            else
+#endif
+            ok = mbar_wait(&bars->pv_done[(g - 1) % kPvRing], ((g - 1) / kPvRing) & 1);
             if (!ok) break;
             tc_fence_after();
-            uint32_t lsum;
-            tmem_ld_x1(tmem + lane_addr + kColL, lsum);
             uint32_t o[32];
             tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&bars->o_free);    // the next item's first product may overwrite O and L now
-            const float l = __uint_as_float(lsum);
+            mbar_arrive(&bars->o_free);    // the next item's first product may overwrite O now
+            // the two halves of the row sum meet through their own slots of the exchange buffer
+            xchg[(4 + half) * 128 + row] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            l += xchg[(4 + (half ^ 1)) * 128 + row];
             const float sink2 = p.sinks ? p.sinks[it.head] * 1.4426950408889634f : neg_inf_f();
             const float Mt = fmaxf(m, sink2);
             const float e = m == neg_inf_f() ? 0.f : ex2(m - Mt);
@@ -442,6 +426,12 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
             ++n_it;
         }
         if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
+#ifdef CC_PREFILL_PROF
+        if (tid == 64) {
+            atomicAdd(&g_prefill_prof[8], static_cast<unsigned long long>(clock64() - soft_t0));
+            atomicAdd(&g_prefill_prof[9], static_cast<unsigned long long>(g));
+        }
+#endif
     }
     tc_fence_before();
     __syncthreads();
@@ -452,6 +442,17 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
 }
 
 }  // namespace
+
+#ifdef CC_PREFILL_PROF
+extern "C" void cc_debug_prefill_prof(unsigned long long *out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_prefill_prof, sizeof(unsigned long long) * 16);
+    if (reset) {
+        unsigned long long zero[16] = {};
+        cudaMemcpyToSymbol(g_prefill_prof, zero, sizeof zero);
+    }
+}
+#endif
 
 void launch_prefill(const PrefillParams &p, cudaStream_t stream) {
     cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
