@@ -41,9 +41,11 @@ KV_HEADS, GROUP, D, PAGE = 8, 8, 64, 16
 WINDOW = 128
 LEN_LO, LEN_HI = 1024, 8192
 
-# DRAM bytes per launch of the full-layer decode kernel from the committed ncu capture
-# (profiles/), filled in after each capture; None until one exists for this workload.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 321_652_480  # profiles/decode_kernel_config2.md: 316.07 MB read + 5.59 MB written
+# DRAM bytes moved per algorithmic byte by the full-layer decode kernel, from the committed ncu
+# capture (profiles/decode_kernel_config2.md: 316.07 MB read + 5.59 MB written for 315.79 MB of
+# algorithmic bytes).  Traffic grows in proportion to the keys read, so a launch's traffic is this
+# ratio times its algorithmic bytes.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 321_652_480 / 315_791_360
 
 
 def algorithmic_bytes(lens: np.ndarray, window: int, kv_heads: int = KV_HEADS) -> int:
@@ -502,7 +504,9 @@ def run_gpu(args):
                     "ms_per_step": e2e_s / args.steps * 1e3, "timed_with": "host clock around K steps, synchronised"},
             "roofline": {"bound": "hbm", "kernel": "decode_kernel (full-causal layer)", "achieved": achieved,
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": full_bytes,
+                         "traffic": int(full_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                         "traffic_source": "ncu capture of a smaller launch, scaled by algorithmic bytes",
+                         "algorithmic_bytes_per_launch": full_bytes,
                          "us_per_launch": k_s / reps * 1e6},
         }
         if prefill is not None:
