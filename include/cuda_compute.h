@@ -103,6 +103,9 @@ typedef struct cc_rope_append_args {
     uint32_t heads;            /* = 8 * kv_heads */
     uint32_t kv_heads;
     uint32_t *status;          /* device word the kernel raises on bad pages/rows; may be NULL */
+    uint32_t q_row_stride;     /* elements between tokens' rows of q; 0 = packed (heads * 64) */
+    uint32_t k_row_stride;     /* same for k; 0 = packed (kv_heads * 64) */
+    uint32_t v_row_stride;     /* same for v: lets q, k, v be column ranges of one projection output */
 } cc_rope_append_args;
 int cc_rope_append_paged(void *stream, const cc_rope_append_args *args);
 
@@ -184,6 +187,37 @@ typedef struct cc_prefill_args {
 } cc_prefill_args;
 int cc_attention_prefill_paged(void *stream, const cc_prefill_args *args);
 
+/* ---- C2. The rest of the attention block, bf16, for the tensor-parallel layout ------------------
+ * (one KV group per GPU: QKV column-parallel, output projection row-parallel, one all-reduce).
+ * Device pointers and a stream, like the raw entries above. */
+
+/* `rms_norm` (gpt-oss/src/model.rs:274-280; Batch::rmsnorm_rows apple.rs:1733-1758):
+ * out = x / sqrt(mean(x^2) + eps) * w; x and out [rows][d] bf16, w [d] float. */
+int cc_rmsnorm_bf16(void *stream, const void *x, const float *w, void *out, uint32_t rows, uint32_t d, float eps);
+
+/* A projection (model.rs:424-429, 465-467; bf16 rows as weights/src/dense.rs:82-94):
+ * out[m][n] = a[m][k] . w[n][k]^T, all bf16 with f32 accumulation; lda, ldw, ldo are the row
+ * strides in elements.  Runs on cuBLASLt, opened on first use. */
+typedef struct cc_blas cc_blas;
+int cc_blas_new(cc_blas **out);
+void cc_blas_free(cc_blas *blas);
+int cc_gemm_bf16(cc_blas *blas, void *stream, const void *a, const void *w, void *out, uint32_t m, uint32_t n,
+                 uint32_t k, uint32_t lda, uint32_t ldw, uint32_t ldo);
+
+/* The residual add after the output projection (Batch::add_rows apple.rs:1886-1911, used at
+ * gpt-oss/src/gpu.rs:807-817): h += o (+ bias), h and o [rows][width] bf16, bias [width] float or
+ * NULL. */
+int cc_residual_add_bf16(void *stream, void *h, const void *o, const float *bias, uint32_t rows, uint32_t width);
+
+/* The block's one collective: the sum over GPUs of the row-parallel output projection.  It has no
+ * counterpart in loadngo (which runs on one device).  NCCL, opened on first use; `id` is NCCL's
+ * 128-byte unique id, made on one rank and handed to the others by the caller. */
+typedef struct cc_comm cc_comm;
+int cc_comm_unique_id(void *id128);
+int cc_comm_init(const void *id128, int world, int rank, cc_comm **out);
+void cc_comm_free(cc_comm *comm);
+int cc_all_reduce_bf16(cc_comm *comm, void *stream, void *buffer, size_t count);
+
 /* ---- D. Gpu, Buffer, Resident -------------------------------------------------------------- */
 
 typedef struct cc_gpu cc_gpu;           /* metal-compute/src/apple.rs:72 `Gpu` */
@@ -215,6 +249,12 @@ void *cc_buffer_as_bytes_mut(cc_buffer *buffer);
 void *cc_buffer_write_range(cc_buffer *buffer, size_t offset, size_t len);
 /* The device address (for raw entries). */
 void *cc_buffer_device_ptr(cc_buffer *buffer);
+/* For callers that mix buffers with the raw entries: flush enqueues, on the gpu's stream, the
+ * upload of what the host wrote since the last upload (a batch does this by itself at commit);
+ * invalidate tells the buffer that a raw kernel wrote `len` bytes at `offset` on the device, so
+ * that the next cc_buffer_as_bytes brings them to the host. */
+int cc_buffer_flush(cc_buffer *buffer);
+int cc_buffer_invalidate(cc_buffer *buffer, size_t offset, size_t len);
 /* Fills the whole buffer with zero bytes on the device (and the mirror). */
 int cc_buffer_zero(cc_buffer *buffer);
 

@@ -1,0 +1,166 @@
+"""One GPU's share of gpt-oss's attention block under tensor parallelism by KV group.
+
+The sequence is the one `GpuModel::encode_attention` records (gpt-oss/src/gpu.rs:703-827):
+RMSNorm of the residual, Q/K/V projections, rotary on Q and K, K/V into the cache, attention, the
+output projection, its sum into the residual.  Here the projections are bf16 GEMMs, rotary and
+append are one kernel, the cache is paged, and the heads are split over GPUs: rank r of N owns KV
+heads `shard_kv_heads(8, N, r)` with their 8 query heads each, the matching rows of W_q, W_k, W_v
+(column-parallel, no communication) and the matching columns of W_o (row-parallel), whose partial
+products are summed over the ranks by the block's one all-reduce.
+
+Only call sequencing lives here; every number is computed by libcuda_compute.so.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from . import compute
+from .layer import PagedAttentionLayer
+from .paged import GROUP, HEAD_DIM, shard_kv_heads
+
+HIDDEN = 2880
+Q_HEADS, KV_HEADS = 64, 8
+
+
+def shard_weights(w_qkv: np.ndarray, w_o: np.ndarray, world: int, rank: int):
+    """Rows of W_qkv ([64*64 q rows | 8*64 k rows | 8*64 v rows] x hidden) and columns of W_o
+    (hidden x 64*64) that rank `rank` of `world` owns, as contiguous arrays."""
+    heads = shard_kv_heads(KV_HEADS, world, rank)
+    q_rows = np.concatenate([np.arange(g * GROUP * HEAD_DIM, (g + 1) * GROUP * HEAD_DIM) for g in heads])
+    k_rows = Q_HEADS * HEAD_DIM + np.concatenate([np.arange(g * HEAD_DIM, (g + 1) * HEAD_DIM) for g in heads])
+    v_rows = k_rows + KV_HEADS * HEAD_DIM
+    local_qkv = np.ascontiguousarray(w_qkv[np.concatenate([q_rows, k_rows, v_rows])])
+    local_o = np.ascontiguousarray(w_o[:, q_rows])
+    return local_qkv, local_o
+
+
+class AttentionBlock:
+    """bf16 attention block for `seqs` sequences on one rank.  `w_qkv`, `w_o` are this rank's
+    shards as bfloat16 bit patterns (uint16), `norm` the RMSNorm weight (f32)."""
+
+    def __init__(self, gpu: compute.Gpu, *, seqs: int, max_context: int, max_tokens: int, w_qkv: np.ndarray,
+                 w_o: np.ndarray, norm: np.ndarray, sinks: np.ndarray, window: int = 0, kv_local: int = KV_HEADS,
+                 comm: int | None = None, eps: float = 1e-5, rng: np.random.Generator | None = None):
+        self.gpu, self.kv_local, self.comm, self.eps = gpu, kv_local, comm, eps
+        self.heads = kv_local * GROUP
+        self.qkv_width = (self.heads + 2 * kv_local) * HEAD_DIM
+        self.att_width = self.heads * HEAD_DIM
+        assert w_qkv.shape == (self.qkv_width, HIDDEN) and w_o.shape == (HIDDEN, self.att_width)
+        self.layer = PagedAttentionLayer(gpu, seqs=seqs, max_context=max_context, max_new=max_tokens,
+                                         kv_heads=kv_local, window=window, sinks=sinks, rng=rng)
+        self.max_tokens = max_tokens
+        self.w_qkv, self.w_o = gpu.upload(w_qkv), gpu.upload(w_o)
+        self.norm = gpu.upload(np.asarray(norm, np.float32))
+        self.h = gpu.buffer(max_tokens * HIDDEN * 2)       # residual stream, replicated on every rank
+        self.x = gpu.buffer(max_tokens * HIDDEN * 2)       # normalised input of the projections
+        self.qkv = gpu.buffer(max_tokens * self.qkv_width * 2)
+        self.o = gpu.buffer(max_tokens * HIDDEN * 2)       # this rank's partial output projection
+        h = ctypes.c_void_p()
+        compute.check(compute.lib().cc_blas_new(ctypes.byref(h)))
+        self.blas = h.value
+        for b in (self.w_qkv, self.w_o, self.norm, self.layer.table, self.layer.sinks):
+            b.flush()
+        self.status = gpu.device_buffer(256)
+        self.status.zero()
+        self.workspace = None
+
+    # -- one pass --------------------------------------------------------------------------------
+    def _launch(self, n: int, *, decode: bool, seqs: int, max_len: int, max_t: int) -> None:
+        L, s, layer = compute.lib(), self.gpu.stream, self.layer
+        kvl, heads = self.kv_local, self.heads
+        check = compute.check
+        check(L.cc_rmsnorm_bf16(s, self.h.device_ptr, self.norm.device_ptr, self.x.device_ptr, n, HIDDEN, self.eps))
+        check(L.cc_gemm_bf16(self.blas, s, self.x.device_ptr, self.w_qkv.device_ptr, self.qkv.device_ptr, n,
+                             self.qkv_width, HIDDEN, HIDDEN, HIDDEN, self.qkv_width))
+        q = self.qkv.device_ptr
+        args = compute.RopeAppendArgs(
+            q, q + heads * HEAD_DIM * 2, q + (heads + kvl) * HEAD_DIM * 2, 0, layer.q_rot.device_ptr,
+            layer.q_rot.device_ptr + n * heads * HEAD_DIM * 2, layer.table.device_ptr, 0, len(layer.table) // 256,
+            layer.positions.device_ptr, layer.seq_ids.device_ptr, layer.cache.pool.device_ptr, layer.cache.pool_pages,
+            layer.cache.table.device_ptr, layer.cache.max_pages, 0, n, heads, kvl, self.status.device_ptr,
+            self.qkv_width, self.qkv_width, self.qkv_width)
+        check(L.cc_rope_append_paged(s, ctypes.byref(args)))
+        sinks = layer.sinks.device_ptr if layer.has_sinks else None
+        qr = layer.q_rot.device_ptr
+        if decode:
+            need = L.cc_decode_workspace_bytes(seqs, kvl, max_len, layer.window, 0)
+            if self.workspace is None or len(self.workspace) < need:
+                self.workspace = self.gpu.device_buffer(max(need, 1 << 20))
+                self.workspace.zero()
+            d = compute.DecodeArgs(qr, qr + n * heads * HEAD_DIM * 2, layer.cache.pool.device_ptr,
+                                   layer.cache.pool_pages, layer.cache.table.device_ptr, layer.cache.max_pages, 0,
+                                   layer.seq_lens.device_ptr, seqs, max_len, sinks, heads, kvl, layer.window,
+                                   layer.scale, layer.out.device_ptr, self.workspace.device_ptr, len(self.workspace),
+                                   0, self.status.device_ptr)
+            check(L.cc_attention_decode_paged(s, ctypes.byref(d)))
+        else:
+            a = compute.PrefillArgs(qr, qr + n * heads * HEAD_DIM * 2, layer.cache.pool.device_ptr,
+                                    layer.cache.pool_pages, layer.cache.table.device_ptr, layer.cache.max_pages, 0,
+                                    layer.q_offsets.device_ptr, layer.starts.device_ptr, seqs, n, max_t, sinks, heads,
+                                    kvl, layer.window, layer.scale, layer.out.device_ptr, self.status.device_ptr)
+            check(L.cc_attention_prefill_paged(s, ctypes.byref(a)))
+        check(L.cc_gemm_bf16(self.blas, s, layer.out.device_ptr, self.w_o.device_ptr, self.o.device_ptr, n, HIDDEN,
+                             self.att_width, self.att_width, self.att_width, HIDDEN))
+        if self.comm is not None:
+            check(L.cc_all_reduce_bf16(self.comm, s, self.o.device_ptr, n * HIDDEN))
+        check(L.cc_residual_add_bf16(s, self.h.device_ptr, self.o.device_ptr, None, n, HIDDEN))
+
+    def _stage_meta(self, positions, seq_ids) -> None:
+        layer = self.layer
+        layer.positions.write(np.asarray(positions, np.int32))
+        layer.seq_ids.write(np.asarray(seq_ids, np.int32))
+        layer.cache.flush_table()
+        for b in (layer.positions, layer.seq_ids, layer.cache.table, layer.seq_lens, layer.q_offsets, layer.starts, self.h):
+            b.flush()
+
+    def prefill(self, hidden: np.ndarray, counts) -> np.ndarray:
+        """`counts[s]` new tokens per sequence (rows of `hidden`, bf16 bits, back to back).  Returns
+        the residual stream after the block (bf16 bits); with a communicator, identical on every rank."""
+        layer = self.layer
+        counts = np.asarray(counts, np.int64)
+        seqs, total = counts.size, int(counts.sum())
+        starts = layer.cache.lens[:seqs].astype(np.int32)
+        for s in range(seqs):
+            layer.cache.reserve(s, int(starts[s] + counts[s]))
+        self.h.write(hidden)
+        layer.q_offsets.write(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+        layer.starts.write(starts)
+        positions = np.concatenate([np.arange(starts[s], starts[s] + counts[s]) for s in range(seqs)])
+        self._stage_meta(positions, np.repeat(np.arange(seqs), counts))
+        self._launch(total, decode=False, seqs=seqs, max_len=0, max_t=int(counts.max()))
+        return self._read_h(total)
+
+    def decode(self, hidden: np.ndarray) -> np.ndarray:
+        """One new token for each of the first `len(hidden)` sequences."""
+        layer = self.layer
+        n = hidden.shape[0]
+        positions = layer.cache.lens[:n].astype(np.int32)
+        for s in range(n):
+            layer.cache.reserve(s, int(positions[s]) + 1)
+        self.h.write(hidden)
+        layer.seq_lens.write((positions + 1).astype(np.int32))
+        self._stage_meta(positions, np.arange(n))
+        self._launch(n, decode=True, seqs=n, max_len=int(positions.max()) + 1, max_t=1)
+        return self._read_h(n)
+
+    def _read_h(self, n: int) -> np.ndarray:
+        self.gpu.synchronize()
+        self.h.invalidate(0, n * HIDDEN * 2)
+        return self.h.view(np.uint16)[: n * HIDDEN].reshape(n, HIDDEN).copy()
+
+    def read_partial(self, n: int) -> np.ndarray:
+        """This rank's output-projection product of the last pass (summed over ranks if there is
+        a communicator), bf16 bits."""
+        self.gpu.synchronize()
+        self.o.invalidate(0, n * HIDDEN * 2)
+        return self.o.view(np.uint16)[: n * HIDDEN].reshape(n, HIDDEN).copy()
+
+    def free(self) -> None:
+        compute.lib().cc_blas_free(self.blas)
+        for b in (self.w_qkv, self.w_o, self.norm, self.h, self.x, self.qkv, self.o, self.status):
+            b.free()
+        if self.workspace is not None:
+            self.workspace.free()
+        self.layer.free()

@@ -92,7 +92,8 @@ class RopeAppendArgs(Structure):
                 ("table_start", c_uint64), ("table_rows", c_uint64), ("positions", c_void_p),
                 ("seq_ids", c_void_p), ("pool", c_void_p), ("pool_pages", c_uint32),
                 ("block_table", c_void_p), ("max_pages", c_uint32), ("ring_pages", c_uint32),
-                ("n", c_uint32), ("heads", c_uint32), ("kv_heads", c_uint32), ("status", c_void_p)]
+                ("n", c_uint32), ("heads", c_uint32), ("kv_heads", c_uint32), ("status", c_void_p),
+                ("q_row_stride", c_uint32), ("k_row_stride", c_uint32), ("v_row_stride", c_uint32)]
 
 
 class DecodeArgs(Structure):
@@ -133,6 +134,16 @@ SYMBOLS = {
     "cc_attention_prefill_paged": (c_int, [c_void_p, POINTER(PrefillArgs)]),
     "cc_attention_decode_paged_static": (c_int, [c_void_p, POINTER(DecodeArgs)]),
     "cc_decode_static_scratch_bytes": (c_size_t, []),
+    "cc_rmsnorm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_float]),
+    "cc_blas_new": (c_int, [POINTER(c_void_p)]),
+    "cc_blas_free": (None, [c_void_p]),
+    "cc_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32,
+                             c_uint32, c_uint32, c_uint32]),
+    "cc_residual_add_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32]),
+    "cc_comm_unique_id": (c_int, [c_void_p]),
+    "cc_comm_init": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
+    "cc_comm_free": (None, [c_void_p]),
+    "cc_all_reduce_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),
     "cc_gpu_new": (c_int, [c_int, POINTER(c_void_p)]),
     "cc_gpu_free": (None, [c_void_p]),
     "cc_gpu_stream": (c_void_p, [c_void_p]),
@@ -146,6 +157,8 @@ SYMBOLS = {
     "cc_buffer_write_range": (c_void_p, [c_void_p, c_size_t, c_size_t]),
     "cc_buffer_device_ptr": (c_void_p, [c_void_p]),
     "cc_buffer_zero": (c_int, [c_void_p]),
+    "cc_buffer_flush": (c_int, [c_void_p]),
+    "cc_buffer_invalidate": (c_int, [c_void_p, c_size_t, c_size_t]),
     "cc_resident_new": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_void_p)]),
     "cc_resident_free": (None, [c_void_p]),
     "cc_resident_len": (c_size_t, [c_void_p]),
@@ -258,6 +271,14 @@ class Buffer:
 
     def zero(self) -> None:
         check(lib().cc_buffer_zero(self._h))
+
+    def flush(self) -> None:
+        """Enqueues the upload of what the host wrote (for use with the raw entries)."""
+        check(lib().cc_buffer_flush(self._h))
+
+    def invalidate(self, offset: int = 0, length: int | None = None) -> None:
+        """Tells the buffer a raw kernel wrote this range on the device."""
+        check(lib().cc_buffer_invalidate(self._h, offset, len(self) - offset if length is None else length))
 
     @property
     def device_ptr(self) -> int:

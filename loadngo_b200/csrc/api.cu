@@ -231,6 +231,12 @@ int rope_append_prepare(const cc_rope_append_args *a, cc::RopeAppendParams *out)
     p.ring_pages = a->ring_pages;
     p.n = a->n; p.heads = a->heads; p.kv_heads = a->kv_heads;
     p.pool_pages = a->pool_pages;
+    p.q_stride = a->q_row_stride ? a->q_row_stride : a->heads * cc::kHeadDim;
+    p.k_stride = a->k_row_stride ? a->k_row_stride : a->kv_heads * cc::kHeadDim;
+    p.v_stride = a->v_row_stride ? a->v_row_stride : a->kv_heads * cc::kHeadDim;
+    if (p.q_stride < a->heads * cc::kHeadDim || p.k_stride < a->kv_heads * cc::kHeadDim ||
+        p.v_stride < a->kv_heads * cc::kHeadDim || p.q_stride % 8 || p.k_stride % 8 || p.v_stride % 8)
+        return fail(CC_DISPATCH, "rope_append: row strides must cover a row and be multiples of 8 elements");
     p.status = a->status;
     *out = p;
     return CC_OK;
@@ -593,6 +599,25 @@ extern "C" void *cc_buffer_write_range(cc_buffer *b, size_t offset, size_t len) 
     return b->host + offset;
 }
 extern "C" void *cc_buffer_as_bytes_mut(cc_buffer *b) { return b ? cc_buffer_write_range(b, 0, b->len) : nullptr; }
+
+extern "C" int cc_buffer_flush(cc_buffer *b) {
+    if (!b) return fail(CC_DISPATCH, "buffer: null");
+    if (b->in_flight.load(std::memory_order_acquire)) return fail(CC_DISPATCH, "buffer: a batch owns it");
+    if (b->host && b->host_dirty_lo < b->host_dirty_hi) {
+        cudaSetDevice(b->gpu->device);
+        CUDA_TRY(cudaMemcpyAsync(b->dev + b->host_dirty_lo, b->host + b->host_dirty_lo,
+                                 b->host_dirty_hi - b->host_dirty_lo, cudaMemcpyHostToDevice, b->gpu->stream));
+        b->host_dirty_lo = b->host_dirty_hi = 0;
+    }
+    return CC_OK;
+}
+
+extern "C" int cc_buffer_invalidate(cc_buffer *b, size_t offset, size_t len) {
+    if (!b) return fail(CC_DISPATCH, "buffer: null");
+    if (offset > b->len || len > b->len - offset) return fail(CC_DISPATCH, "buffer: range outside it");
+    if (len) mark(b->dev_dirty_lo, b->dev_dirty_hi, offset, offset + len);
+    return CC_OK;
+}
 
 extern "C" int cc_buffer_zero(cc_buffer *b) {
     if (!b) return fail(CC_DISPATCH, "buffer: null");

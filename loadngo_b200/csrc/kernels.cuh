@@ -31,6 +31,7 @@ struct RopeAppendParams {
     uint32_t ring_pages;          // 0: page = block_table[seq][pos/16]; else [(pos/16) % ring_pages]
     uint32_t n, heads, kv_heads;
     uint32_t pool_pages;
+    uint32_t q_stride, k_stride, v_stride;  // elements between consecutive tokens' rows of q, k, v
     uint32_t *status;             // device error word (0 = ok)
 };
 void launch_rope_append(const RopeAppendParams &p, cudaStream_t stream);

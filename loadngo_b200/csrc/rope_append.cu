@@ -73,10 +73,11 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         const float *cs_row = p.table + row * (kHeadDim / 2) * 2;
         if (j < q_items) {
             const uint32_t head = j >> 2, c = j & 3;
-            const size_t base = (static_cast<size_t>(token) * p.heads + head) * kHeadDim + c * 8;
+            const size_t base = (static_cast<size_t>(token) * p.heads + head) * kHeadDim + c * 8;   // q_hi / q_lo rows
+            const size_t src = static_cast<size_t>(token) * p.q_stride + head * kHeadDim + c * 8;
             float a[8], b[8];
-            load8<F32>(p.q, base, a);
-            load8<F32>(p.q, base + 32, b);
+            load8<F32>(p.q, src, a);
+            load8<F32>(p.q, src + 32, b);
             rotate8(a, b, cs_row + c * 16);
             uint4 ha = pack8(a), hb = pack8(b);
             *reinterpret_cast<uint4 *>(p.q_hi + base) = ha;
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         j -= q_items;
         if (j < k_items) {
             const uint32_t head = j >> 2, c = j & 3;
-            const size_t base = (static_cast<size_t>(token) * p.kv_heads + head) * kHeadDim + c * 8;
+            const size_t base = static_cast<size_t>(token) * p.k_stride + head * kHeadDim + c * 8;
             float a[8], b[8];
             load8<F32>(p.k, base, a);
             load8<F32>(p.k, base + 32, b);
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         } else {
             j -= k_items;
             const uint32_t head = j >> 3, c = j & 7;
-            const size_t base = (static_cast<size_t>(token) * p.kv_heads + head) * kHeadDim + c * 8;
+            const size_t base = static_cast<size_t>(token) * p.v_stride + head * kHeadDim + c * 8;
             float x[8];
             load8<F32>(p.v, base, x);
             uint16_t *dst = p.pool +
