@@ -388,6 +388,217 @@ class PrefillBench:
             layer.free()
 
 
+# ------------------------------------------------------------------------------------------
+# Other BASELINE configurations, run on request (--workload); each prints its own JSON line
+# ------------------------------------------------------------------------------------------
+def _dist_setup():
+    """Rank bookkeeping and a gloo group for the few host-side exchanges these modes need."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("gloo")
+    return torch, dist, world, rank, local
+
+
+def _max_over_ranks(dist, world, x: float) -> float:
+    if world == 1:
+        return x
+    import torch
+    t = torch.tensor([x], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_longctx(args):
+    """BASELINE config 4: long-context decode through a 36-layer stack (even layers 128-window, odd
+    full, gpt-oss/src/config.rs:101-103), batch 64, KV lengths uniform in [32768, 131072] (seed 0),
+    KV sharded by KV head over N GPUs, no collective.  Total work is fixed (strong scaling).  The
+    18 full layers share one physical cache per GPU and the 18 window layers another: the values
+    are synthetic and one layer's cache is far larger than L2, so the timing is that of 36 distinct
+    caches while set-up stays short and the N=1 point fits in memory (said in DESIGN.md)."""
+    from loadngo_b200 import compute
+    from loadngo_b200.layer import PagedAttentionLayer
+    from loadngo_b200.paged import shard_kv_heads
+    from oracle import oracle
+    torch, dist, world, rank, local = _dist_setup()
+    gpu = compute.Gpu(local)
+    kvl = len(shard_kv_heads(KV_HEADS, world, rank))
+    heads = kvl * GROUP
+    seqs, layers = 64, 36
+    lens = np.random.default_rng(0).integers(32768, 131073, seqs).astype(np.int64)
+    steps_total = args.warmup + args.steps + 1
+    rng = np.random.default_rng(5)
+    stack = []
+    for window in (WINDOW, 0):
+        pool_pages = int(sum(-(-(int(l) + steps_total) // PAGE) for l in lens)) + 4
+        layer = PagedAttentionLayer(gpu, seqs=seqs, max_context=int(lens.max()) + steps_total, max_new=seqs,
+                                    kv_heads=kvl, window=window, sinks=rng.standard_normal(heads).astype(np.float32),
+                                    pool_pages=pool_pages, rng=rng)
+        for s, length in enumerate(lens):
+            layer.cache.reserve(s, int(length) + steps_total)
+        layer.cache.lens[:] = lens
+        layer.cache.flush_table()
+        # one random 64 MiB block repeated through the pool: N(0,1) everywhere, set-up in seconds
+        nbytes = len(layer.cache.pool)
+        chunk = min(64 << 20, nbytes)
+        stage = gpu.upload(oracle.f32_to_bf16_bits(rng.standard_normal(chunk // 2).astype(np.float32)))
+        done = 0
+        while done < nbytes:
+            size = min(chunk, nbytes - done)
+            b = gpu.batch([stage, layer.cache.pool])
+            b.copy_rows((compute.Slice(0, 0, size), size // 4), (compute.Slice(1, done, size), size // 4), 1, size // 4)
+            r = b.run()
+            if isinstance(r.gpu_time, Exception):
+                raise r.gpu_time
+            done += size
+        stage.free()
+        bf = lambda shape: oracle.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32))
+        layer.q.write(bf((seqs, heads, D))); layer.k.write(bf((seqs, kvl, D))); layer.v.write(bf((seqs, kvl, D)))
+        layer.seq_ids.write(np.arange(seqs, dtype=np.int32))
+        pos_all = (lens[None, :] + np.arange(steps_total)[:, None]).astype(np.int32)
+        layer.positions.free(); layer.seq_lens.free()
+        layer.positions = gpu.upload(pos_all)
+        layer.seq_lens = gpu.upload(pos_all + 1)
+        stack.append(layer)
+
+    def run(first, steps):
+        bufs = stack[0].buffers() + stack[1].buffers()
+        nb = len(stack[0].buffers())
+        batch = gpu.batch(bufs)
+        for i in range(steps):
+            step = first + i
+            for l in range(layers):
+                layer = stack[l % 2]
+                base = (l % 2) * nb
+                S = lambda j, off, ln: compute.Slice(base + j, off, ln)
+                cache = compute.PagedCache(S(layer.POOL, 0, len(layer.cache.pool)), S(layer.BT, 0, len(layer.cache.table)),
+                                           layer.cache.max_pages, 0, kvl)
+                n = seqs
+                batch.rope_append_paged((S(layer.Q, 0, n * heads * D * 2), S(layer.K, 0, n * kvl * D * 2),
+                                         S(layer.V, 0, n * kvl * D * 2)), False, S(layer.QROT, 0, 2 * n * heads * D * 2),
+                                        S(layer.TABLE, 0, len(layer.table)), 0, S(layer.POS, step * n * 4, n * 4),
+                                        S(layer.SEQ, 0, n * 4), cache, n)
+                batch.attention_decode_paged(S(layer.QROT, 0, 2 * n * heads * D * 2), cache,
+                                             S(layer.LENS, step * n * 4, n * 4), n, int(lens.max()) + step + 1,
+                                             S(layer.SINKS, 0, heads * 4), layer.window, layer.scale,
+                                             S(layer.OUT, 0, n * heads * D * 2))
+        launches = batch.dispatches
+        r = batch.run()
+        if isinstance(r.gpu_time, Exception):
+            raise r.gpu_time
+        return r.gpu_time, launches
+
+    run(0, args.warmup)
+    if world > 1:
+        dist.barrier()
+    sec, launches = run(args.warmup, args.steps)
+    sec = _max_over_ranks(dist, world, sec)
+    step_lens = lens + args.warmup + 1
+    total_bytes = 18 * (algorithmic_bytes(step_lens, 0) + algorithmic_bytes(step_lens, WINDOW))   # all 8 KV heads
+    peak, peak_kind = measured_peak()
+    if rank == 0:
+        gbs = total_bytes * args.steps / sec / 1e9
+        print(json.dumps({
+            "workload": "long-context decode, 36-layer gpt-oss-120b-shape attention stack, batch 64, KV uniform "
+                        "[32768,131072], KV sharded by KV head", "metric": "decode attn HBM GB/s", "value": gbs,
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": sec / args.steps * 1e3, "scaling": "strong", "per_gpu_gbs": gbs / world,
+            "frac_of_hbm_peak_per_gpu": gbs / world / peak, "peak": peak, "peak_source": peak_kind,
+            "tok_s": seqs * args.steps / sec, "gpu_launches": launches,
+            "note": "the 18 full layers alias one physical cache per GPU, the 18 window layers another"}), flush=True)
+    if world > 1:
+        dist.barrier()
+
+
+def run_block(args):
+    """BASELINE config 5: the whole attention block with tensor parallelism by KV group: RMSNorm,
+    bf16 QKV GEMM (2880 -> 5120, column-parallel), RoPE + append, sink attention, output projection
+    (4096 -> 2880, row-parallel), NCCL all-reduce, residual.  Weights N(0, 0.02), hidden N(0,1),
+    16 x 2048-token prefill then 128 decode steps."""
+    from loadngo_b200 import compute
+    from loadngo_b200.block import HIDDEN, AttentionBlock, shard_weights
+    from oracle import oracle
+    import ctypes
+    torch, dist, world, rank, local = _dist_setup()
+    gpu = compute.Gpu(local)
+    L = compute.lib()
+    comm = None
+    if world > 1:
+        ident = (ctypes.c_ubyte * 128)()
+        if rank == 0:
+            compute.check(L.cc_comm_unique_id(ident))
+        box = [bytes(ident)]
+        dist.broadcast_object_list(box, src=0)
+        h = ctypes.c_void_p()
+        compute.check(L.cc_comm_init(box[0], world, rank, ctypes.byref(h)))
+        comm = h.value
+    rng = np.random.default_rng(7)   # same weights and inputs on every rank
+    seqs, T, decode_steps = 16, 2048, 128
+    w_qkv = (rng.standard_normal((5120, HIDDEN)) * 0.02).astype(np.float32)
+    w_o = (rng.standard_normal((HIDDEN, 4096)) * 0.02).astype(np.float32)
+    norm = (1.0 + rng.standard_normal(HIDDEN) * 0.02).astype(np.float32)
+    sinks = rng.standard_normal(64).astype(np.float32)
+    lq, lo = shard_weights(w_qkv, w_o, world, rank)
+    kvl = KV_HEADS // world
+    block = AttentionBlock(gpu, seqs=seqs, max_context=T + decode_steps + 8, max_tokens=seqs * T,
+                           w_qkv=oracle.f32_to_bf16_bits(lq), w_o=oracle.f32_to_bf16_bits(lo), norm=norm,
+                           sinks=sinks[rank * kvl * GROUP:(rank + 1) * kvl * GROUP], kv_local=kvl, comm=comm)
+    hidden = oracle.f32_to_bf16_bits(rng.standard_normal((seqs * T, HIDDEN)).astype(np.float32))
+    stream = torch.cuda.ExternalStream(gpu.stream)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+
+    def sync():
+        gpu.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    # prefill: one timed pass (the cache is reset before it)
+    block.prefill(hidden, [T] * seqs)             # warm-up pass (cuBLASLt heuristics, NCCL channels)
+    for s in range(seqs):
+        block.layer.truncate(s, 0)
+    plan = block.stage_prefill(hidden, [T] * seqs)
+    sync()
+    ev[0].record(stream)
+    block.launch(plan)
+    ev[1].record(stream)
+    sync()
+    prefill_ms = _max_over_ranks(dist, world, ev[0].elapsed_time(ev[1]))
+    hd = hidden[:seqs]
+    for _ in range(3):
+        block.decode(hd)
+    sync()
+    decode_ms = 0.0
+    for _ in range(decode_steps - 3):
+        plan = block.stage_decode(hd)
+        gpu.synchronize()
+        ev[2].record(stream)
+        block.launch(plan)
+        ev[3].record(stream)
+        gpu.synchronize()
+        decode_ms += ev[2].elapsed_time(ev[3])
+    sync()
+    decode_ms = _max_over_ranks(dist, world, decode_ms) / (decode_steps - 3)
+    if rank == 0:
+        m = seqs * T
+        flops = 2 * m * 5120 * HIDDEN + 2 * m * HIDDEN * 4096 + 4 * D * 64 * (T * (T + 1) // 2) * seqs
+        print(json.dumps({
+            "workload": "gpt-oss-20b attention block, tensor parallel by KV group: RMSNorm, bf16 QKV GEMM, RoPE+append, "
+                        "sink attention, O projection, NCCL all-reduce; 16 x 2048 prefill then 128 decode steps",
+            "n_gpus": world, "prefill_ms": prefill_ms, "prefill_tflops_whole_job": flops / prefill_ms / 1e9,
+            "prefill_tokens_per_s": m / prefill_ms * 1e3, "decode_ms_per_step": decode_ms,
+            "decode_tokens_per_s": seqs / decode_ms * 1e3, "all_reduce_bytes_prefill": m * HIDDEN * 2,
+            "timed_with": "CUDA events on the launching stream around the block's kernels (inputs staged before), max over ranks",
+            "collective": "ncclAllReduce bf16 sum" if world > 1 else "none (1 GPU)"}), flush=True)
+    if comm is not None:
+        L.cc_comm_free(comm)
+    if world > 1:
+        dist.barrier()
+
+
 def measured_tensor_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -533,6 +744,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "longctx", "block"],
+                    help="decode: the headline (config 2); longctx: config 4; block: config 5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (config 3) section")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill (config 3) section")
@@ -542,6 +755,10 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "longctx":
+        run_longctx(args)
+    elif args.workload == "block":
+        run_block(args)
     else:
         run_gpu(args)
 

@@ -115,9 +115,9 @@ class AttentionBlock:
         for b in (layer.positions, layer.seq_ids, layer.cache.table, layer.seq_lens, layer.q_offsets, layer.starts, self.h):
             b.flush()
 
-    def prefill(self, hidden: np.ndarray, counts) -> np.ndarray:
-        """`counts[s]` new tokens per sequence (rows of `hidden`, bf16 bits, back to back).  Returns
-        the residual stream after the block (bf16 bits); with a communicator, identical on every rank."""
+    def stage_prefill(self, hidden: np.ndarray, counts) -> dict:
+        """Puts `counts[s]` new tokens per sequence (rows of `hidden`, bf16 bits, back to back) and
+        their positions into the block's buffers; returns what `launch` needs."""
         layer = self.layer
         counts = np.asarray(counts, np.int64)
         seqs, total = counts.size, int(counts.sum())
@@ -129,10 +129,9 @@ class AttentionBlock:
         layer.starts.write(starts)
         positions = np.concatenate([np.arange(starts[s], starts[s] + counts[s]) for s in range(seqs)])
         self._stage_meta(positions, np.repeat(np.arange(seqs), counts))
-        self._launch(total, decode=False, seqs=seqs, max_len=0, max_t=int(counts.max()))
-        return self._read_h(total)
+        return dict(n=total, decode=False, seqs=seqs, max_len=0, max_t=int(counts.max()))
 
-    def decode(self, hidden: np.ndarray) -> np.ndarray:
+    def stage_decode(self, hidden: np.ndarray) -> dict:
         """One new token for each of the first `len(hidden)` sequences."""
         layer = self.layer
         n = hidden.shape[0]
@@ -142,8 +141,23 @@ class AttentionBlock:
         self.h.write(hidden)
         layer.seq_lens.write((positions + 1).astype(np.int32))
         self._stage_meta(positions, np.arange(n))
-        self._launch(n, decode=True, seqs=n, max_len=int(positions.max()) + 1, max_t=1)
-        return self._read_h(n)
+        return dict(n=n, decode=True, seqs=n, max_len=int(positions.max()) + 1, max_t=1)
+
+    def launch(self, plan: dict) -> None:
+        """Enqueues the block's kernels for what was staged (returns at once)."""
+        self._launch(plan["n"], decode=plan["decode"], seqs=plan["seqs"], max_len=plan["max_len"], max_t=plan["max_t"])
+
+    def prefill(self, hidden: np.ndarray, counts) -> np.ndarray:
+        """Stage, launch, and return the residual stream after the block (bf16 bits); with a
+        communicator the result is identical on every rank."""
+        plan = self.stage_prefill(hidden, counts)
+        self.launch(plan)
+        return self._read_h(plan["n"])
+
+    def decode(self, hidden: np.ndarray) -> np.ndarray:
+        plan = self.stage_decode(hidden)
+        self.launch(plan)
+        return self._read_h(plan["n"])
 
     def _read_h(self, n: int) -> np.ndarray:
         self.gpu.synchronize()
