@@ -1,0 +1,143 @@
+"""Host-side logic without a GPU: page bookkeeping (the session state of the reference's
+GpuSession: len / truncate / reset), KV-head and weight sharding, the byte accounting of the
+benchmark, and the multi-rank plumbing of bench.py over gloo with two CPU processes."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+from loadngo_b200 import paged
+from loadngo_b200.block import shard_weights
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class FakeBuffer:
+    def __init__(self, n):
+        self.n, self.written = n, None
+
+    def __len__(self):
+        return self.n
+
+    def zero(self):
+        pass
+
+    def write(self, array, offset=0):
+        self.written = np.array(array, copy=True)
+
+
+class FakeGpu:
+    def buffer(self, n):
+        return FakeBuffer(n)
+
+    device_buffer = buffer
+
+
+def test_pages_are_reserved_truncated_and_reset():
+    cache = paged.PagedKvCache(FakeGpu(), seqs=2, max_pages=8, pool_pages=10, kv_heads=8)
+    assert len(cache.pool) == 10 * 8 * 4096
+    cache.reserve(0, 17)                       # positions 0..16 -> 2 pages
+    cache.reserve(1, 16)                       # exactly one page
+    assert (cache.table_host[0] >= 0).sum() == 2 and (cache.table_host[1] >= 0).sum() == 1
+    assert cache.lens.tolist() == [17, 16] and len(cache.free) == 7
+    cache.reserve(0, 18)                       # same page: nothing new
+    assert len(cache.free) == 7
+    pages = set(cache.table_host[cache.table_host >= 0].tolist())
+    assert len(pages) == 3                     # no page handed out twice
+    cache.truncate(0, 16)                      # Session::truncate (model.rs:204-213): back to 16 positions
+    assert cache.lens[0] == 16 and (cache.table_host[0] >= 0).sum() == 1 and len(cache.free) == 8
+    cache.truncate(0, 40)                      # truncating forward is a no-op
+    assert cache.lens[0] == 16
+    with pytest.raises(ValueError):
+        cache.reserve(0, 8 * 16 + 1)           # more than max_pages
+    cache.reserve(0, 8 * 16)
+    with pytest.raises(MemoryError):
+        cache.reserve(1, 5 * 16)               # pool exhausted: 10 pages, 8 + 1 used
+    cache.reset()
+    assert cache.lens.tolist() == [0, 0] and len(cache.free) == 10 and (cache.table_host < 0).all()
+    cache.flush_table()
+    assert cache.table.written.shape == (2, 8)
+
+
+def test_ring_of_pages_wraps_like_the_reference_ring_of_slots():
+    # gpt-oss/src/gpu.rs:567-574: a sliding layer keeps window + chunk rows; here 12 pages
+    cache = paged.PagedKvCache(FakeGpu(), seqs=1, max_pages=12, pool_pages=12, kv_heads=1, ring_pages=12)
+    cache.reserve(0, 5000)
+    assert (cache.table_host[0] >= 0).sum() == 12 and cache.lens[0] == 5000
+    cache.truncate(0, 4990)                    # within what the ring still holds
+    with pytest.raises(ValueError):
+        cache.truncate(0, 100)                 # long overwritten (gpu.rs:397-412 refuses the same)
+
+
+def test_kv_heads_and_weights_shard_without_overlap():
+    for world in (1, 2, 4, 8):
+        seen = []
+        for rank in range(world):
+            seen += list(paged.shard_kv_heads(8, world, rank))
+        assert seen == list(range(8))
+    with pytest.raises(ValueError):
+        paged.shard_kv_heads(8, 3, 0)
+    w_qkv = np.arange(5120 * 4, dtype=np.float32).reshape(5120, 4)
+    w_o = np.arange(3 * 4096, dtype=np.float32).reshape(3, 4096)
+    for world in (2, 8):
+        rows, cols = [], []
+        for rank in range(world):
+            lq, lo = shard_weights(w_qkv, w_o, world, rank)
+            kvl = 8 // world
+            assert lq.shape == ((8 + 2) * kvl * 64, 4) and lo.shape == (3, kvl * 512)
+            rows += lq[:, 0].astype(int).tolist()
+            cols += lo[0].astype(int).tolist()
+            # rank's q rows are its groups' heads, then its k heads, then its v heads
+            g0 = rank * kvl
+            assert lq[0, 0] == g0 * 512 * 4 and lq[kvl * 512, 0] == (4096 + g0 * 64) * 4
+            assert lq[kvl * 576, 0] == (4608 + g0 * 64) * 4
+        assert sorted(rows) == list(range(0, 5120 * 4, 4)) and sorted(cols) == list(range(4096))
+
+
+def test_benchmark_byte_accounting():
+    sys.path.insert(0, ROOT)
+    import bench
+    lens = np.array([1024, 8192])
+    # per (sequence, layer): 2048 n + 8192 (q) + 8192 (out) + 4096 (new k, v read and written)
+    assert bench.algorithmic_bytes(lens, 0) == 2048 * (1024 + 8192) + 2 * 20480
+    assert bench.algorithmic_bytes(lens, 128) == 2048 * 256 + 2 * 20480
+    assert bench.algorithmic_bytes(lens, 0, kv_heads=1) * 8 == bench.algorithmic_bytes(lens, 0)
+    drawn = bench.draw_lengths(32)
+    assert drawn.min() >= 1024 and drawn.max() <= 8192 and np.array_equal(drawn, bench.draw_lengths(32))
+
+
+def test_two_ranks_over_gloo_agree_on_time_and_share_an_id():
+    """world_size 2 on CPU: what bench.py does between ranks (max of the timings, one rank's
+    128-byte communicator id handed to the others, the reference arm running on rank 0 only)."""
+    script = textwrap.dedent(f"""
+        import os, sys
+        sys.path.insert(0, {ROOT!r})
+        import torch.distributed as dist
+        import bench
+        from loadngo_b200.paged import shard_kv_heads
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        assert bench._max_over_ranks(dist, world, 1.0 + rank) == 2.0
+        box = [bytes([7] * 128) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        assert box[0] == bytes([7] * 128)
+        heads = list(shard_kv_heads(8, world, rank))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, heads)
+        assert sum(gathered, []) == list(range(8))
+        dist.barrier()
+        print("rank", rank, "ok")
+    """)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, "-c", script], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert all("ok" in o for o in outs)
+    # the reference arm under a multi-rank launch: rank 1 exits without work or output
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
+                         env=dict(env, RANK="1", LOCAL_RANK="1"), capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and out.stdout.strip() == ""
