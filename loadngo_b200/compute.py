@@ -183,6 +183,7 @@ SYMBOLS = {
     "cc_batch_read_back": (c_int, [c_void_p, Slice]),
     "cc_batch_commit": (c_int, [c_void_p, COMPLETION_FN, c_void_p]),
     "cc_batch_commit_wait": (c_int, [c_void_p, POINTER(c_double)]),
+    "cc_batch_replay_wait": (c_int, [c_void_p, POINTER(c_double)]),
     "cc_batch_drop": (None, [c_void_p]),
     "cc_batch_dispatches": (c_uint32, [c_void_p]),
 }
@@ -463,6 +464,14 @@ class Batch:
         seconds = c_double()
         h, self._h = self._h, None
         code = lib().cc_batch_commit_wait(h, byref(seconds))
+        if code != 0:
+            return Completed(self._buffers, _ERRORS.get(code, Error)(lib().cc_last_error().decode()))
+        return Completed(self._buffers, seconds.value)
+
+    def replay(self) -> Completed:
+        """Runs what is recorded and waits, keeping the batch for further replays."""
+        seconds = c_double()
+        code = lib().cc_batch_replay_wait(self._h, byref(seconds))
         if code != 0:
             return Completed(self._buffers, _ERRORS.get(code, Error)(lib().cc_last_error().decode()))
         return Completed(self._buffers, seconds.value)

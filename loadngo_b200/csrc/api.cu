@@ -670,6 +670,7 @@ struct cc_batch {
     std::vector<cc_slice> read_backs;
     std::vector<cc_slice> outputs;  // ranges the recorded work writes; marked device-newer at commit
     uint32_t dispatches = 0;
+    bool replayed = false;
 };
 
 namespace {
@@ -1102,9 +1103,11 @@ namespace {
 
 // Uploads what the host changed, runs the recorded work, copies requested ranges back, and
 // queues the completion.  Consumes the batch.
-int submit(cc_batch *b, cc_completion_fn done, void *user) {
+int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false) {
     cc_gpu *gpu = b->gpu;
     cudaSetDevice(gpu->device);
+    if (keep)   // a replay takes its buffers again (they came back when the last run completed)
+        for (cc_buffer *buf : b->buffers) buf->in_flight.store(true, std::memory_order_release);
     Pending job;
     job.done = done;
     job.user = user;
@@ -1113,7 +1116,7 @@ int submit(cc_batch *b, cc_completion_fn done, void *user) {
     if (e == cudaSuccess) e = cudaEventCreate(&job.end);
     if (e != cudaSuccess) {
         for (cc_buffer *buf : b->buffers) buf->in_flight.store(false, std::memory_order_release);
-        delete b;
+        if (!keep) delete b;
         return cuda_fail(e, "batch events");
     }
     cudaStream_t s = gpu->stream;
@@ -1151,7 +1154,7 @@ int submit(cc_batch *b, cc_completion_fn done, void *user) {
         gpu->queue.push_back(std::move(job));
     }
     gpu->cv.notify_all();
-    delete b;
+    if (!keep) delete b;
     return CC_OK;
 }
 
@@ -1185,6 +1188,21 @@ extern "C" int cc_batch_commit_wait(cc_batch *b, double *gpu_seconds) {
     if (!b) return fail(CC_DISPATCH, "commit: null batch");
     WaitBox box;
     if (int rc = submit(b, wait_done, &box)) return rc;
+    std::unique_lock<std::mutex> lock(box.mu);
+    box.cv.wait(lock, [&] { return box.ready; });
+    if (gpu_seconds) *gpu_seconds = box.seconds;
+    if (box.status != CC_OK) return fail(static_cast<cc_status>(box.status), "%s", box.message.c_str());
+    return CC_OK;
+}
+
+extern "C" int cc_batch_replay_wait(cc_batch *b, double *gpu_seconds) {
+    if (!b) return fail(CC_DISPATCH, "replay: null batch");
+    for (cc_buffer *buf : b->buffers)
+        if (buf->in_flight.load(std::memory_order_acquire) && !b->replayed)
+            break;   // first run: the batch has owned its buffers since cc_batch_begin
+    b->replayed = true;
+    WaitBox box;
+    if (int rc = submit(b, wait_done, &box, true)) return rc;
     std::unique_lock<std::mutex> lock(box.mu);
     box.cv.wait(lock, [&] { return box.ready; });
     if (gpu_seconds) *gpu_seconds = box.seconds;

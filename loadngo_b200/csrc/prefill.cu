@@ -8,34 +8,47 @@
 // denominator only (model.rs:449-455).  The new positions' keys and values are already in
 // the paged cache (the fused RoPE + append kernel ran first).
 //
-// A work item = 128 queries of one head.  CTAs are persistent (one per SM): each walks its own
-// fixed sequence of items (heaviest first, the 8 heads of a KV group next to each other so that
-// they share K and V through L2), and its pipelines run on across item boundaries: while the
-// softmax warps finish one item, the producer is already loading the next item's Q, K and V and
-// the tensor core is already computing its first scores.  Eleven warps, four roles:
-//   warp 0  producer: TMA loads of the Q tile (hi and lo planes, double-buffered) and, per
-//           128-key tile, eight 16-key pages of K and of V, found through the block table, into
-//           rings (sixteen lanes look up and issue one page each);
-//   warp 1  one thread issues the score products S = Qhi K^T + Qlo K^T (tcgen05.mma M128 N128 K64
-//           twice) into one of two S buffers in TMEM, up to two tiles ahead of the products;
-//   warp 10 one thread issues O += P V (M128 N64 K128, P read from TMEM) into the O accumulator
-//           in TMEM.  Every tcgen05.mma costs about 60 cycles of tensor pipe however narrow it is
-//           (measured), so nothing small rides on the tensor core (the row sums stay with the
-//           softmax threads), and the two streams have an issuer each so that one thread's
-//           barrier traffic never leaves the pipe empty;
-//   warps 2-9  softmax: two threads per query row, each owning 64 of the tile's 128 keys.  A
-//           thread reads its half of the S row from TMEM, masks edge tiles, shares the row
-//           maximum with its partner through shared memory, writes P = exp2(s - m) as bf16
-//           back into tensor memory over the scores it came from (the products read their A
-//           operand from TMEM, so P never touches shared memory, whose bandwidth the Q K^T
-//           operands already use), and rescales its half of the O row (and the L column) in TMEM when the maximum moved
-//           by more than 2^8; at the end of an item it folds the sink in, normalises and stores
-//           64 bytes of bf16 output.
+// At head_dim 64 the exponentials bound this kernel, not the products: a 128 x 128 score tile
+// needs 16 384 exp2 (1 024 cycles of the SM's 16-lane special-function unit) against about 820
+// cycles of tensor pipe (measured: 8 score instructions of ~56 cycles, 8 product instructions of
+// ~46).  Measured too, and shaping what follows: a tcgen05.commit is seen by a waiting thread
+// about 440 cycles after the last instruction it covers was issued, so every hand-over through
+// the tensor pipe is expensive; four softmax warps per scheduler are needed to keep the exp2
+// unit near its rate (one warp alone reaches half); and the softmax warps' loops have to stay
+// small and rolled (fully unrolled sweeps ran 1.4x slower, out of the instruction cache).
+//
+// A work item = 256 consecutive queries of one head = two query tiles, A and B, of 128 rows.
+// CTAs are persistent (one per SM) and walk a fixed sequence of items, heaviest first, the 8
+// heads of a KV group next to each other so that they share K and V through L2.  Every 128-key
+// tile of K and V that an item needs is loaded once and used by both query tiles, which halves
+// the traffic from L2 into shared memory.  The unit of work inside the CTA is a job = (query
+// tile, key tile); all roles enumerate the same job sequence n = 0, 1, 2, ... (per key tile: A's
+// job, then B's, where the tile is in that query tile's range).  Nineteen warps, four roles:
+//   warp 0   producer: TMA loads of the query tiles (hi and lo planes) into a ring of three
+//            slots, and per key tile sixteen 16-key pages (eight of K, eight of V, found through
+//            the block table, one per lane) into a ring of three stages;
+//   warp 1   one thread issues the scores of job n, S = Qhi K^T + Qlo K^T (tcgen05.mma
+//            M128 N128 K64 twice), into score buffer n mod 3 in tensor memory.  That buffer held
+//            the P of job n - 3: the scores wait only until that job's product has been ISSUED
+//            (the pipe runs what it is given in order), not until it has finished;
+//   warp 18  one thread issues the products O_A or O_B += P V (M128 N64 K128, P read from
+//            tensor memory) as soon as a job's P is published;
+//   warps 2-9 (tile A) and 10-17 (tile B)  softmax, two threads per query row, 64 keys each: a
+//            first sweep over the thread's scores in tensor memory finds their maximum, the two
+//            threads of a row compare through shared memory, a second sweep computes
+//            P = exp2(s - m), sums the rounded weights and writes them as bf16 over the first
+//            half of the scores they came from.  The two tiles' warps drift half a job apart, so
+//            one tile's waits, first sweep and publishing run under the other's exponentials.
+//            O is rescaled only when a row maximum moved by more than 2^8 (rare after the first
+//            tiles); at the end of an item the two halves of the row sum meet, the sink is folded
+//            in and each thread normalises and stores its 64 bytes of the bf16 output row.
 // Tiles entirely outside a query tile's causal / window range are never visited (the loop
 // bounds exclude them, as kernels.metal:631-634 does); only edge tiles are masked per element.
 //
-// Every mbarrier wait is bounded; a wait that runs out raises the status word and the CTA
-// drains, frees its TMEM and returns.
+// Every wait is bounded; one that runs out raises the status word and the CTA drains, frees its
+// TMEM and returns.  A wait on an mbarrier names a phase by its parity, so no role may wait more
+// than one phase ahead of a barrier: where one query tile has no rows for a while (ragged
+// sequences), its warps hold back until the other tile's warps have caught up (`seen`).
 #include "kernels.cuh"
 #include "ptx.cuh"
 #include "tcgen05.cuh"
@@ -44,95 +57,192 @@ namespace cc {
 namespace {
 
 constexpr int kTileQ = 128, kTileK = 128;
-constexpr int kStagesKV = 3;                               // K tile + V tile per stage
-constexpr int kPvRing = 6;                                  // "product done" barriers, by tile index mod 6
-constexpr int kThreadsPrefill = 352;
-constexpr int kSoftmaxThreads = 256;
+constexpr int kQSlots = 3;                                  // ring of query tiles (hi plane + lo plane each)
+constexpr int kStagesKV = 3;                                // K tile + V tile per stage
+constexpr int kSBufs = 3;                                   // score / P buffers in tensor memory
+constexpr int kPvRing = 8;                                  // "product done" barriers, by job index mod 8
+constexpr int kThreadsPrefill = 608;                        // producer, score issuer, 16 softmax warps, product issuer
+constexpr int kPvWarp = 18;
 constexpr int kPlaneBytes = kTileQ * kHeadDim * 2;          // 16 KiB: 128 rows of 128 bytes
-constexpr int kOffQ = 0;                                    // 2 buffers of (hi plane, lo plane)
-constexpr int kOffKV = 2 * 2 * kPlaneBytes;                 // per stage: K tile then V tile
-constexpr int kOffXchg = kOffKV + kStagesKV * 2 * kPlaneBytes;    // [2 tiles in flight + 1 for row sums][2 halves][128 rows] f32
-constexpr int kOffBars = kOffXchg + 3 * 2 * 128 * 4;
+constexpr int kOffQ = 0;
+constexpr int kOffKV = kQSlots * 2 * kPlaneBytes;
+constexpr int kOffXchg = kOffKV + kStagesKV * 2 * kPlaneBytes;   // [2 query tiles][2 parities][2 halves][128 rows] f32
+constexpr int kOffBars = kOffXchg + 2 * 2 * 2 * 128 * 4;
 constexpr int kSeqCache = 512;                              // sequences whose offsets are kept in shared memory
-constexpr int kOffSeq = kOffBars + 256;                     // q_offsets[0..n] then starts[0..n-1]
+constexpr int kOffSeq = kOffBars + 512;                     // q_offsets[0..n] then starts[0..n-1]
 constexpr int kPrefillSmem = kOffSeq + (2 * kSeqCache + 1) * 4 + 1024;
-// TMEM columns: S0 0-127, S1 128-255 (P(g) overwrites the first 64 columns of S(g)'s buffer as
-// packed bf16 pairs once both threads of every row hold their scores in registers), O 256-319.
+static_assert(kPrefillSmem <= 232448, "shared memory per CTA");
+// TMEM columns: score buffers 0-127, 128-255, 256-383 (each softmax thread writes its 32 columns
+// of packed bf16 P over the first half of the 64 score columns it owns, behind its own reads);
+// O of query tile A 384-447, of tile B 448-511.
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 256;
+constexpr uint32_t kColO = 384;
 constexpr float kRescaleThreshold = 8.0f;                   // log2 domain
 
 struct Bars {
-    uint64_t q_full[2], q_empty[2];
+    uint64_t q_full[kQSlots], q_empty[kQSlots];
     uint64_t kv_full[kStagesKV];
-    uint64_t s_full[2], p_full[2];
-    uint64_t pv_done[kPvRing];   // tile g's product: frees its K/V stage, its P columns, and O for a rescale
-    uint64_t o_free;
+    uint64_t s_full[kSBufs], p_full[kSBufs];
+    uint64_t pv_issued[kPvRing]; // job n's product is in the tensor pipe's queue: the scores of job n + 3 may follow it
+    uint64_t pv_done[kPvRing];   // job n's product: frees its P columns, maybe its K/V stage, and O for a rescale
+    uint64_t o_free[2];          // per query tile: the item's O rows are in registers
+    uint64_t pair[2][4];         // per query tile and lane quarter: both threads of every row have written the exchange buffer
+    uint32_t seen[2];            // per query tile: jobs whose scores its softmax warps have seen arrive
     uint32_t tmem_base;
     uint32_t pad;
 };
-static_assert(sizeof(Bars) <= 256, "barrier block");
-
-__device__ __forceinline__ float neg_inf_f() { return __int_as_float(0xff800000); }
+static_assert(sizeof(Bars) <= 512, "barrier block");
 
 // Optional cycle accounting of where each role waits (built only with -DCC_PREFILL_PROF).
 #ifdef CC_PREFILL_PROF
 __device__ unsigned long long g_prefill_prof[16];
-#define PROF_T0() const long long prof_t0_ = clock64()
-#define PROF_ADD(slot) atomicAdd(&g_prefill_prof[slot], static_cast<unsigned long long>(clock64() - prof_t0_))
-#define PROF_WAIT(slot, expr) [&] { const long long t_ = clock64(); const bool r_ = (expr); \
-    atomicAdd(&g_prefill_prof[slot], static_cast<unsigned long long>(clock64() - t_)); return r_; }()
+__device__ long long g_prefill_trace[4 * 48 * 6];   // CTA 0, the four softmax warps of lane quarter 2: per job, six timestamps
+__device__ long long g_prefill_trace2[3 * 96];   // CTA 0: per job, when its scores were issued, when its product was issued, when the score issuer saw the product of n-3 done
+#define TRACE2(k, n) do { if (blockIdx.x == 0 && (n) < 96) g_prefill_trace2[(k) * 96 + (n)] = clock64(); } while (0)
+#define TRACE(k) do { if (blockIdx.x == 0 && lane == 0 && quarter == 2 && own_jobs <= 48) g_prefill_trace[((grp * 2 + half) * 48 + (own_jobs - 1)) * 6 + (k)] = clock64(); } while (0)
+#define PROF_ON (threadIdx.x == 64 || threadIdx.x == 0 || threadIdx.x == 32 || threadIdx.x == 576)
+#define PROF_DECL unsigned long long prof_acc[16] = {}
+#define PROF_PARAM , unsigned long long (&prof_acc)[16]
+#define PROF_ARG , prof_acc
 #define PROF_BEGIN(name) const long long name = clock64()
-#define PROF_END(slot, name) atomicAdd(&g_prefill_prof[slot], static_cast<unsigned long long>(clock64() - name))
+#define PROF_END(slot, name) prof_acc[slot] += static_cast<unsigned long long>(clock64() - name)
+#define PROF_COUNT(slot) prof_acc[slot] += 1ull
+#define PROF_FAIL(cond, site, num) do { if (!(cond)) { atomicOr(&g_prefill_prof[9], 1ull << (site)); if (atomicCAS(&g_prefill_prof[10], 0ull, static_cast<unsigned long long>(site)) == 0ull) { g_prefill_prof[11] = static_cast<unsigned long long>(num) * 1000ull + blockIdx.x; } } } while (0)
+#define PROF_FLUSH() do { if (PROF_ON) { _Pragma("unroll") for (int i_ = 0; i_ < 16; ++i_) if (prof_acc[i_]) atomicAdd(&g_prefill_prof[i_], prof_acc[i_]); } } while (0)
 #else
+#define PROF_DECL
+#define PROF_PARAM
+#define PROF_ARG
 #define PROF_BEGIN(name)
 #define PROF_END(slot, name)
-#define PROF_T0()
-#define PROF_ADD(slot)
-#define PROF_WAIT(slot, expr) (expr)
+#define PROF_COUNT(slot)
+#define TRACE(k)
+#define TRACE2(k, n)
+#define PROF_FAIL(cond, site, num)
+#define PROF_FLUSH()
 #endif
 
-// One work item: 128 queries (fewer at a sequence's end) of one head.
+__device__ __forceinline__ float neg_inf_f() { return __int_as_float(0xff800000); }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// One work item: 256 queries (fewer at a sequence's end) of one head, as query tiles 0 (A) and 1 (B).
 struct Item {
     bool valid;
     int head, kv_head, seq;
-    int row0;        // first row of the sequence in q / out
-    int t;           // new positions of the sequence
-    int q0;          // first query of this tile within them
-    int end;         // start + t: keys beyond are not there
-    int first_pos, last_pos;
-    int kt_lo, n_tiles;
+    int row0;            // first row of the sequence in q / out
+    int t;               // new positions of the sequence
+    int q0;              // first query of tile A within them
+    int end;             // start + t: keys beyond are not there
+    int first_pos[2], last_pos[2];
+    int lo[2], hi[2];    // key tiles of each query tile (hi < lo: the tile has no rows)
+    int t_lo, t_hi;      // key tiles of the item
 };
 
 // `q_offsets` and `starts` point at the shared-memory copies when the sequences fit there: item
-// boundaries sit on the tensor-core thread's critical path and must not wait on global loads.
+// boundaries sit on the tensor-core threads' critical path and must not wait on global loads.
 __device__ __forceinline__ Item make_item(const PrefillParams &p, const int32_t *q_offsets, const int32_t *starts,
                                           int id, int n_qt) {
     Item it;
     it.head = id % static_cast<int>(p.heads);
     const int r = id / static_cast<int>(p.heads);
-    const int q_tile = n_qt - 1 - (r % n_qt);   // long tiles first
-    it.seq = r / n_qt;
+    it.seq = r % static_cast<int>(p.seqs);
+    const int q_tile = n_qt - 1 - r / static_cast<int>(p.seqs);   // long items first
     it.kv_head = it.head / kGroup;
     it.row0 = q_offsets[it.seq];
     it.t = q_offsets[it.seq + 1] - it.row0;
-    it.q0 = q_tile * kTileQ;
+    it.q0 = q_tile * 2 * kTileQ;
     it.valid = it.q0 < it.t;
     const int start = starts[it.seq];
     it.end = start + it.t;
-    it.first_pos = start + it.q0;
-    it.last_pos = start + min(it.q0 + kTileQ, it.t) - 1;
     const int W = static_cast<int>(p.window);
-    const int key_lo = (W != 0 && it.first_pos + 1 > W) ? it.first_pos + 1 - W : 0;
-    it.kt_lo = key_lo / kTileK;
-    it.n_tiles = it.valid ? it.last_pos / kTileK - it.kt_lo + 1 : 0;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const int q_first = it.q0 + g * kTileQ;
+        it.first_pos[g] = start + q_first;
+        it.last_pos[g] = start + min(q_first + kTileQ, it.t) - 1;
+        const int key_lo = (W != 0 && it.first_pos[g] + 1 > W) ? it.first_pos[g] + 1 - W : 0;
+        const bool rows = q_first < it.t;
+        it.lo[g] = rows ? key_lo / kTileK : 1;
+        it.hi[g] = rows ? it.last_pos[g] / kTileK : 0;
+    }
+    it.t_lo = it.lo[0];
+    it.t_hi = it.hi[1] >= it.lo[1] ? it.hi[1] : it.hi[0];
     return it;
+}
+
+// The softmax of one job for one query row (one thread): scores in `s_addr` (128 columns of this
+// thread's TMEM lane), P written over their first 64 columns.  `lo_col..hi_col` are the visible
+// columns of the row in this key tile (used on edge tiles only).
+// A softmax thread owns 64 of a job's 128 score columns of its query row.  Both sweeps are
+// loops of 32-column chunks, rolled on purpose: with the sweeps fully unrolled the straight-line
+// code of the softmax warps no longer fitted the instruction cache and ran 1.4x slower.
+constexpr int kColsPerThread = 64;
+
+// First sweep: the maximum of this thread's scores.  `col0` is the tile column of the first one;
+// `lo_col..hi_col` are the visible columns of the row in this key tile (used on edge tiles only).
+template <bool kEdge>
+__device__ __forceinline__ float row_max_sweep(uint32_t s_addr, int col0, int lo_col, int hi_col) {
+    float mx0 = neg_inf_f(), mx1 = neg_inf_f(), mx2 = neg_inf_f(), mx3 = neg_inf_f();
+#pragma unroll 1
+    for (int c = 0; c < kColsPerThread / 32; ++c) {
+        uint32_t s[32];
+        tmem_ld_x32(s_addr + c * 32, s);
+        tmem_wait_ld();
+        if (kEdge) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int col = col0 + c * 32 + i;
+                if (col > hi_col || col < lo_col) s[i] = 0xff800000u;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+            mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+            mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+        }
+    }
+    return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+
+// Second sweep: P = exp2(s * scale - m) as packed bf16 pairs, written to `p_addr` (32 columns,
+// behind the scores already read); returns the sum of the rounded weights, the ones the product uses.
+template <bool kEdge>
+__device__ __forceinline__ float exp_sweep(uint32_t s_addr, uint32_t p_addr, int col0, int lo_col, int hi_col, float scale,
+                                           float m_use) {
+    const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
+    float2 l_acc = make_float2(0.f, 0.f);
+#pragma unroll 1
+    for (int c = 0; c < kColsPerThread / 32; ++c) {
+        uint32_t s[32], w[16];
+        tmem_ld_x32(s_addr + c * 32, s);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            if (kEdge) {
+                const int col = col0 + c * 32 + 2 * e;
+                if (col > hi_col || col < lo_col) s[2 * e] = 0xff800000u;
+                if (col + 1 > hi_col || col + 1 < lo_col) s[2 * e + 1] = 0xff800000u;
+            }
+            const float2 x = ffma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), scale2, neg_m2);
+            const uint32_t pair = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
+            w[e] = pair;
+            l_acc = fadd2(l_acc, make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u)));
+        }
+        tmem_st_x16(p_addr + c * 16, w);
+    }
+    return l_acc.x + l_acc.y;
 }
 
 __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __grid_constant__ PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_qt = (static_cast<int>(p.max_t) + kTileQ - 1) / kTileQ;
+    const int n_qt = (static_cast<int>(p.max_t) + 2 * kTileQ - 1) / (2 * kTileQ);
     const int n_items = static_cast<int>(p.seqs) * n_qt * static_cast<int>(p.heads);
     const int W = static_cast<int>(p.window);
 
@@ -142,15 +252,24 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
     const uint32_t smem_base = smem_u32(smem);
 
     if (warp == 0 && lane == 0) {
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kQSlots; ++b) {
             mbar_init(&bars->q_full[b], 1);
             mbar_init(&bars->q_empty[b], 1);
+        }
+        for (int b = 0; b < kSBufs; ++b) {
             mbar_init(&bars->s_full[b], 1);
-            mbar_init(&bars->p_full[b], kSoftmaxThreads);
+            mbar_init(&bars->p_full[b], 8);
         }
         for (int s = 0; s < kStagesKV; ++s) mbar_init(&bars->kv_full[s], 1);
-        for (int s = 0; s < kPvRing; ++s) mbar_init(&bars->pv_done[s], 1);
-        mbar_init(&bars->o_free, kSoftmaxThreads);
+        for (int s = 0; s < kPvRing; ++s) {
+            mbar_init(&bars->pv_done[s], 1);
+            mbar_init(&bars->pv_issued[s], 1);
+        }
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(&bars->o_free[g], 8);
+            for (int q = 0; q < 4; ++q) mbar_init(&bars->pair[g][q], 2);
+            bars->seen[g] = 0;
+        }
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -170,24 +289,35 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    PROF_DECL;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         const int pg = lane & 7;
         const bool is_v = lane >= 8;
         bool ok = true;
-        int n_it = 0, g = 0;
+        int qs = 0, gt = 0, n = 0;
+        int last_job[kStagesKV];   // last job that reads the tile held by each stage
+#pragma unroll
+        for (int s = 0; s < kStagesKV; ++s) last_job[s] = -1;
         for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
             const Item it = make_item(p, q_offsets, starts, id, n_qt);
             if (!it.valid) continue;
-            const int qb = n_it & 1;
             if (lane == 0) {
-                if (n_it >= 2) ok = mbar_wait(&bars->q_empty[qb], ((n_it >> 1) - 1) & 1);
-                if (ok) {
-                    uint8_t *q_dst = smem + kOffQ + qb * 2 * kPlaneBytes;
-                    mbar_expect_tx(&bars->q_full[qb], 2 * kPlaneBytes);
-                    tma_load_3d(q_dst, &p.q_hi_map, 0, it.head, it.row0 + it.q0, &bars->q_full[qb]);
-                    tma_load_3d(q_dst + kPlaneBytes, &p.q_lo_map, 0, it.head, it.row0 + it.q0, &bars->q_full[qb]);
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    if (it.hi[g] < it.lo[g] || !ok) continue;
+                    const int slot = qs % kQSlots;
+                    if (qs >= kQSlots) ok = mbar_wait(&bars->q_empty[slot], (qs / kQSlots - 1) & 1);
+                    PROF_FAIL(ok, 1, qs);
+                    if (ok) {
+                        uint8_t *q_dst = smem + kOffQ + slot * 2 * kPlaneBytes;
+                        const int row = it.row0 + it.q0 + g * kTileQ;
+                        mbar_expect_tx(&bars->q_full[slot], 2 * kPlaneBytes);
+                        tma_load_3d(q_dst, &p.q_hi_map, 0, it.head, row, &bars->q_full[slot]);
+                        tma_load_3d(q_dst + kPlaneBytes, &p.q_lo_map, 0, it.head, row, &bars->q_full[slot]);
+                    }
+                    ++qs;
                 }
             }
             const int32_t *table_row = p.block_table + static_cast<size_t>(it.seq) * p.max_pages;
@@ -206,15 +336,21 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                 }
                 return y;
             };
-            int y_next = lookup(it.kt_lo);
-            for (int j = 0; j < it.n_tiles; ++j, ++g) {
-                const int stage = g % kStagesKV;
+            int y_next = lookup(it.t_lo);
+            for (int kt = it.t_lo; kt <= it.t_hi; ++kt, ++gt) {
+                const int stage = gt % kStagesKV;
                 const int y = y_next;
-                if (j + 1 < it.n_tiles) y_next = lookup(it.kt_lo + j + 1);   // in flight while this tile is issued
+                if (kt < it.t_hi) y_next = lookup(kt + 1);   // in flight while this tile is issued
+                int prev = -1;
+#pragma unroll
+                for (int s = 0; s < kStagesKV; ++s)
+                    if (s == stage) prev = last_job[s];
                 if (lane == 0) {
-                    // the stage is free once the product of the tile that used it (g - 3) is done
-                    if (g >= kStagesKV)
-                        ok = PROF_WAIT(10, mbar_wait(&bars->pv_done[(g - kStagesKV) % kPvRing], ((g - kStagesKV) / kPvRing) & 1));
+                    // the stage is free once the last product that read its previous tile is done
+                    PROF_BEGIN(t_st);
+                    if (prev >= 0) ok = mbar_wait(&bars->pv_done[prev % kPvRing], (prev / kPvRing) & 1);
+                    PROF_END(15, t_st);
+                    PROF_FAIL(ok, 2, gt);
                     if (ok) mbar_expect_tx(&bars->kv_full[stage], 2 * kPlaneBytes);
                 }
                 ok = __all_sync(0xffffffffu, ok);   // also orders the expect_tx before the loads below
@@ -222,198 +358,284 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                 if (lane < 16)
                     tma_load_2d(smem + kOffKV + stage * 2 * kPlaneBytes + (is_v ? kPlaneBytes : 0) + pg * 2048, &p.pool_map,
                                 0, y, &bars->kv_full[stage]);
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+                    if (kt >= it.lo[g] && kt <= it.hi[g]) ++n;
+#pragma unroll
+                for (int s = 0; s < kStagesKV; ++s)
+                    if (s == stage) last_job[s] = n - 1;
             }
-            ++n_it;
         }
         if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
         __syncwarp();
-    } else if (warp == 1 || warp == 10) {
-        // ------------------------------------------- two MMA issuers: warp 1 scores, warp 10 products
-        // Each walks the CTA's item sequence on its own.  One thread issuing everything spent more
-        // time on barrier waits and commits between its instructions than the tensor pipe needs
-        // to run them; with two issuers the pipe always has the other stream's work queued.
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ score issuer (one thread)
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileQ, kTileK, false);
-            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true);
-            const bool scores = warp == 1;
             bool ok = true;
-            int n_it = 0, g = 0;
-            PROF_T0();
+            int qs = 0, gt = 0, n = 0;
             for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
                 const Item it = make_item(p, q_offsets, starts, id, n_qt);
                 if (!it.valid) continue;
-                const int qb = n_it & 1;
-                if (scores) {
-                    ok = PROF_WAIT(0, mbar_wait(&bars->q_full[qb], (n_it >> 1) & 1));
-                    const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + qb * 2 * kPlaneBytes, 16, 1024);
-                    const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
-                    for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
-                        const int stage = g % kStagesKV;
-                        ok = PROF_WAIT(1, mbar_wait(&bars->kv_full[stage], (g / kStagesKV) & 1));
-                        // S(g) goes where P(g - 2) was: that product must have read it
-                        if (ok && g >= 2) ok = PROF_WAIT(2, mbar_wait(&bars->pv_done[(g - 2) % kPvRing], ((g - 2) / kPvRing) & 1));
+                int slot[2];
+                bool q_ready[2] = {false, false};
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    slot[g] = qs;
+                    if (it.hi[g] >= it.lo[g]) ++qs;
+                }
+                for (int kt = it.t_lo; kt <= it.t_hi && ok; ++kt, ++gt) {
+                    const int stage = gt % kStagesKV;
+                    PROF_BEGIN(t_kv);
+                    ok = mbar_wait(&bars->kv_full[stage], (gt / kStagesKV) & 1);
+                    PROF_END(12, t_kv);
+                    PROF_FAIL(ok, 3, gt);
+                    const uint64_t k_desc = smem_desc_sw128(smem_base + kOffKV + stage * 2 * kPlaneBytes, 16, 1024);
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        if (kt < it.lo[g] || kt > it.hi[g] || !ok) continue;
+                        const int sl = slot[g] % kQSlots;
+                        if (!q_ready[g]) {
+                            ok = mbar_wait(&bars->q_full[sl], (slot[g] / kQSlots) & 1);
+                            PROF_FAIL(ok, 4, n);
+                            q_ready[g] = true;
+                        }
+                        // S(n) goes where P(n - 3) was.  The tensor pipe runs what it is given in order,
+                        // so that product only has to have been issued (not finished) before these scores
+                        // are: the fences on both sides of the barrier order the two threads' instructions.
+                        PROF_BEGIN(t_sf);
+                        if (ok && n >= kSBufs)
+                            ok = mbar_wait(&bars->pv_issued[(n - kSBufs) % kPvRing], ((n - kSBufs) / kPvRing) & 1);
+                        PROF_END(13, t_sf);
+                        PROF_FAIL(ok, 5, n);
                         if (!ok) break;
                         tc_fence_after();
-                        const uint64_t k_desc = smem_desc_sw128(smem_base + kOffKV + stage * 2 * kPlaneBytes, 16, 1024);
-                        const uint32_t d = tmem + static_cast<uint32_t>(g & 1) * kTileK;
+                        const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + sl * 2 * kPlaneBytes, 16, 1024);
+                        const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
+                        const uint32_t d = tmem + static_cast<uint32_t>(n % kSBufs) * kTileK;
+                        TRACE2(2, n);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qhi_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks > 0);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qlo_desc + ks * 2, k_desc + ks * 2, idesc_qk, true);
-                        umma_commit(&bars->s_full[g & 1]);
-                    }
-                    if (ok) umma_commit(&bars->q_empty[qb]);   // all scores of this item are issued
-                } else {
-                    // the first product of an item overwrites O: the previous item's rows must be out
-                    if (n_it > 0) ok = PROF_WAIT(3, mbar_wait(&bars->o_free, (n_it - 1) & 1));
-                    for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
-                        const int stage = g % kStagesKV, b = g & 1;
-                        ok = PROF_WAIT(4, mbar_wait(&bars->p_full[b], (g >> 1) & 1));
-                        if (ok) ok = mbar_wait(&bars->kv_full[stage], (g / kStagesKV) & 1);   // long since there
-                        if (!ok) break;
-                        tc_fence_after();
-                        // P comes from tensor memory: 16 keys of a k-step are 8 columns of packed bf16 pairs
-                        const uint32_t p_tmem = tmem + static_cast<uint32_t>(b) * kTileK;
-                        const uint64_t v_desc =
-                            smem_desc_sw128(smem_base + kOffKV + stage * 2 * kPlaneBytes + kPlaneBytes, 1024, 1024);
-#pragma unroll
-                        for (int ks = 0; ks < 8; ++ks)
-                            umma_bf16_ts(tmem + kColO, p_tmem + ks * 8, v_desc + ks * (2048 >> 4), idesc_pv, j > 0 || ks > 0);
-                        umma_commit(&bars->pv_done[g % kPvRing]);
+                        TRACE2(0, n);
+                        umma_commit(&bars->s_full[n % kSBufs]);
+                        if (kt == it.hi[g]) umma_commit(&bars->q_empty[sl]);   // all scores of this query tile are issued
+                        ++n;
                     }
                 }
-                ++n_it;
             }
             if (!ok) raise_status(p.status, kStatusWaitTimeout);
-            PROF_ADD(5);
+        }
+        __syncwarp();
+    } else if (warp == kPvWarp) {
+        // ---------------------------------------------------------- product issuer (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileQ, kHeadDim, true);
+            bool ok = true;
+            int gt = 0, n = 0;
+            int items_of[2] = {0, 0};   // items in which each query tile had rows
+            for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
+                const Item it = make_item(p, q_offsets, starts, id, n_qt);
+                if (!it.valid) continue;
+                bool first[2] = {true, true};
+                for (int kt = it.t_lo; kt <= it.t_hi && ok; ++kt, ++gt) {
+                    const int stage = gt % kStagesKV;
+                    const uint64_t v_desc =
+                        smem_desc_sw128(smem_base + kOffKV + stage * 2 * kPlaneBytes + kPlaneBytes, 1024, 1024);
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        if (kt < it.lo[g] || kt > it.hi[g] || !ok) continue;
+                        // the first product of an item overwrites O: the previous item's rows must be out
+                        if (first[g] && items_of[g] > 0) ok = mbar_wait(&bars->o_free[g], (items_of[g] - 1) & 1);
+                        PROF_FAIL(ok, 6, n);
+                        PROF_BEGIN(t_pf);
+                        if (ok) ok = mbar_wait(&bars->p_full[n % kSBufs], (n / kSBufs) & 1);
+                        PROF_END(14, t_pf);
+                        PROF_FAIL(ok, 7, n);
+                        if (ok) ok = mbar_wait(&bars->kv_full[stage], (gt / kStagesKV) & 1);   // long since there
+                        if (!ok) break;
+                        tc_fence_after();
+                        // P comes from tensor memory: 16 keys of a k-step are 8 columns of packed bf16 pairs;
+                        // keys 0-63 sit in columns 0-31 of the buffer, keys 64-127 in columns 64-95
+                        const uint32_t p_tmem = tmem + static_cast<uint32_t>(n % kSBufs) * kTileK;
+                        const uint32_t o_tmem = tmem + kColO + static_cast<uint32_t>(g) * kHeadDim;
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks)
+                            umma_bf16_ts(o_tmem, p_tmem + (ks >> 2) * 64 + (ks & 3) * 8, v_desc + ks * (2048 >> 4), idesc_pv, !first[g] || ks > 0);
+                        umma_commit(&bars->pv_done[n % kPvRing]);
+                        tc_fence_before();
+                        mbar_arrive(&bars->pv_issued[n % kPvRing]);
+                        TRACE2(1, n);
+                        first[g] = false;
+                        ++n;
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+                    if (it.hi[g] >= it.lo[g]) ++items_of[g];
+            }
+            if (!ok) raise_status(p.status, kStatusWaitTimeout);
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------- softmax, two threads per row (64 keys each)
+        // ------------------------------------- softmax, two threads per query row (64 keys each)
+        const int sw = warp - 2;                      // 0..15
         const int quarter = warp & 3;                 // the TMEM lanes this warp can reach
-        const int half = (warp - 2) >> 2;             // which 64 of the tile's 128 keys, which 32 of O's 64 columns
+        const int grp = sw >> 3;                      // query tile A or B
+        const int half = (sw >> 2) & 1;               // which 64 of a tile's 128 keys, which 32 of O's 64 columns
         const int row = quarter * 32 + lane;          // row of the query tile
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        float *xchg = reinterpret_cast<float *>(smem + kOffXchg);
+        const uint32_t o_addr = tmem + lane_addr + kColO + static_cast<uint32_t>(grp * kHeadDim + half * 32);
+        float *xchg = reinterpret_cast<float *>(smem + kOffXchg) + grp * (2 * 2 * 128);
+        uint64_t *pair_bar = &bars->pair[grp][quarter];
         const float scale = p.scale_log2e;
         bool ok = true;
-        int n_it = 0, g = 0;
-#ifdef CC_PREFILL_PROF
-        const long long soft_t0 = clock64();
-#endif
+        int n = 0;
+        uint32_t meets = 0;    // exchanges with the row's other thread so far
+        uint32_t own_jobs = 0, other_jobs = 0;
+        volatile uint32_t *seen_own = &bars->seen[grp], *seen_other = &bars->seen[grp ^ 1];
+        PROF_BEGIN(t_soft);
+        // Both threads of a row leave their value in the exchange buffer and pick up the other's.
+        auto exchange = [&](float mine, float &theirs) -> bool {
+            const uint32_t par = meets & 1;
+            xchg[(par * 2 + half) * 128 + row] = mine;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pair_bar);
+            const bool met = __all_sync(0xffffffffu, mbar_wait(pair_bar, par));
+            theirs = xchg[(par * 2 + (half ^ 1)) * 128 + row];
+            ++meets;
+            return met;
+        };
         for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x) {
             const Item it = make_item(p, q_offsets, starts, id, n_qt);
             if (!it.valid) continue;
-            const int pos = it.first_pos + row;       // absolute position of this query
+            const int my_first = grp ? it.first_pos[1] : it.first_pos[0];
+            const int my_last = grp ? it.last_pos[1] : it.last_pos[0];
+            const int pos = my_first + row;                // absolute position of this query
             const int vis_lo = (W != 0 && pos + 1 > W) ? pos + 1 - W : 0;
             float m = neg_inf_f(), l = 0.f;   // l: this thread's half of the row sum
-            for (int j = 0; j < it.n_tiles; ++j, ++g) {
-                const int b = g & 1;
-#ifdef CC_PREFILL_PROF
-                if (tid == 64) ok = PROF_WAIT(6, mbar_wait(&bars->s_full[b], (g >> 1) & 1));
-                else
-#endif
-                ok = mbar_wait(&bars->s_full[b], (g >> 1) & 1);
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t s[2][32];
+            int prev_own = -1;
+            for (int kt = it.t_lo; kt <= it.t_hi && ok; ++kt) {
 #pragma unroll
-                for (int c = 0; c < 2; ++c) tmem_ld_x32(tmem + lane_addr + b * kTileK + half * 64 + c * 32, s[c]);
-                tmem_wait_ld();
-                const int kt = it.kt_lo + j;
-                const int key0 = kt * kTileK + half * 64;
-                const bool edge = (kt * kTileK + kTileK - 1 > it.first_pos) || (W != 0 && kt * kTileK + W <= it.last_pos);
-                if (edge) {
-#pragma unroll
-                    for (int c = 0; c < 2; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int key = key0 + c * 32 + i;
-                            if (key > pos || key < vis_lo) s[c][i] = 0xff800000u;
+                for (int g = 0; g < 2; ++g) {
+                    if (kt < it.lo[g] || kt > it.hi[g] || !ok) continue;
+                    if (g != grp) {
+                        ++other_jobs;
+                        ++n;
+                        continue;
+                    }
+                    const int b = n % kSBufs;
+                    PROF_BEGIN(t_s);
+                    // A wait on an mbarrier names a phase by its parity only, so it must not be
+                    // made more than one phase early: the other query tile's softmax has to have
+                    // seen the scores of all its earlier jobs (the last users of this buffer among
+                    // them) before this one's are waited for.  Matters when one tile has no rows
+                    // for a while and its warps run ahead.
+                    if (*seen_other < other_jobs) {
+                        const long long began = clock64();
+                        while (*seen_other < other_jobs && ok) {
+                            __nanosleep(64);
+                            if (clock64() - began > kWaitCycles) ok = false;
                         }
-                }
-                float mx = neg_inf_f();
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        mx = fmaxf(mx, fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
-                // the row maximum over both halves: through shared memory, one named barrier per tile
-                xchg[(b * 2 + half) * 128 + row] = mx;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                mx = fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * 128 + row]);
-                const float m_cand = fmaxf(m, mx * scale);
-                // keep the old maximum unless it moved by more than 2^8: fewer trips through TMEM
-                const bool move = (m_cand > m + kRescaleThreshold) || (m == neg_inf_f() && m_cand > m);
-                const float m_new = move ? m_cand : m;
-                const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
-                const float alpha = move ? ex2(m - m_use) : 1.0f;
-                m = m_new;
-                l *= alpha;
-                // Only a rescale has to wait for the previous tile's P V product; the common case
-                // goes straight on to its exponentials while that product is still running.
-                if (j > 0 && __any_sync(0xffffffffu, move)) {
-                    ok = mbar_wait(&bars->pv_done[(g - 1) % kPvRing], ((g - 1) / kPvRing) & 1);
+                        ok = __all_sync(0xffffffffu, ok);
+                        PROF_FAIL(ok, 8, n);
+                        if (!ok) break;
+                    }
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (n / kSBufs) & 1));
+                    ++own_jobs;
+                    if ((sw & 7) == 0 && lane == 0) *seen_own = own_jobs;
+                    TRACE(0);
+                    PROF_END(0, t_s);
+                    PROF_FAIL(ok, 9, n);
                     if (!ok) break;
                     tc_fence_after();
-                    uint32_t o[32];
-                    tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
-                    tmem_wait_ld();
+                    PROF_BEGIN(t_p1);
+                    const uint32_t s_addr = tmem + lane_addr + static_cast<uint32_t>(b * kTileK + half * kColsPerThread);
+                    const uint32_t p_addr = s_addr;   // P goes over this thread's own scores, behind the reads
+                    const int col0 = half * kColsPerThread;
+                    const int lo_col = vis_lo - kt * kTileK, hi_col = pos - kt * kTileK;
+                    const bool edge = (kt * kTileK + kTileK - 1 > my_first) || (W != 0 && kt * kTileK + W <= my_last);
+                    float mx = edge ? row_max_sweep<true>(s_addr, col0, lo_col, hi_col)
+                                    : row_max_sweep<false>(s_addr, col0, lo_col, hi_col);
+                    PROF_END(1, t_p1);
+                    TRACE(1);
+                    PROF_BEGIN(t_x);
+                    float mx_other;
+                    ok = exchange(mx, mx_other);
+                    PROF_END(2, t_x);
+                    TRACE(2);
+                    PROF_FAIL(ok, 10, n);
+                    if (!ok) break;
+                    mx = fmaxf(mx, mx_other);
+                    const float m_cand = fmaxf(m, mx * scale);
+                    // keep the old maximum unless it moved by more than 2^8: fewer trips through TMEM
+                    const bool move = (m_cand > m + kRescaleThreshold) || (m == neg_inf_f() && m_cand > m);
+                    const float m_new = move ? m_cand : m;
+                    const float m_use = m_new == neg_inf_f() ? 0.f : m_new;
+                    const float alpha = move ? ex2(m - m_use) : 1.0f;
+                    m = m_new;
+                    l *= alpha;
+                    // Only a rescale has to wait for this query tile's previous product.
+                    if (prev_own >= 0 && __any_sync(0xffffffffu, move)) {
+                        PROF_BEGIN(t_rs);
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[prev_own % kPvRing], (prev_own / kPvRing) & 1));
+                        if (!ok) break;
+                        tc_fence_after();
+                        uint32_t o[32];
+                        tmem_ld_x32(o_addr, o);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st_x32(tmem + lane_addr + kColO + half * 32, o);
-                    tmem_wait_st();
-                }
-                // P = exp2(s * scale - m) as packed bf16 pairs, written over this row's scores in
-                // tensor memory (every thread of the CTA holds its scores in registers since the
-                // barrier above; the tensor core reads P before it overwrites the buffer again).
-                const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
-                uint32_t w[32];
-                float l_acc[2] = {0.f, 0.f};
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float2 x = ffma2(make_float2(__uint_as_float(s[c][2 * e]), __uint_as_float(s[c][2 * e + 1])),
-                                               scale2, neg_m2);
-                        const uint32_t pair = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
-                        w[c * 16 + e] = pair;
-                        // the denominator sums the rounded weights, the ones the product uses
-                        l_acc[e & 1] += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_x32(o_addr, o);
+                        tmem_wait_st();
+
                     }
+                    TRACE(3);
+                    PROF_BEGIN(t_ex);
+                    l += edge ? exp_sweep<true>(s_addr, p_addr, col0, lo_col, hi_col, scale, m_use)
+                              : exp_sweep<false>(s_addr, p_addr, col0, lo_col, hi_col, scale, m_use);
+                    PROF_END(4, t_ex);
+                    TRACE(4);
+                    PROF_BEGIN(t_pub);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->p_full[b]);
+                    PROF_END(5, t_pub);
+                    TRACE(5);
+                    PROF_COUNT(8);
+                    prev_own = n;
+                    ++n;
                 }
-                l += l_acc[0] + l_acc[1];
-                tmem_st_x32(tmem + lane_addr + b * kTileK + half * 32, w);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&bars->p_full[b]);
             }
             if (!ok) break;
-            // ---- the item's rows: wait for its last product, read O and L, hand them back, store
-#ifdef CC_PREFILL_PROF
-            if (tid == 64) ok = PROF_WAIT(7, mbar_wait(&bars->pv_done[(g - 1) % kPvRing], ((g - 1) / kPvRing) & 1));
-            else
-#endif
-            ok = mbar_wait(&bars->pv_done[(g - 1) % kPvRing], ((g - 1) / kPvRing) & 1);
+            if (prev_own < 0) continue;   // this query tile has no rows in this item
+            // ---- the item's rows: wait for the last product, read O, hand the accumulator back, store
+            PROF_BEGIN(t_epi);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[prev_own % kPvRing], (prev_own / kPvRing) & 1));
+            PROF_FAIL(ok, 12, n);
             if (!ok) break;
             tc_fence_after();
             uint32_t o[32];
-            tmem_ld_x32(tmem + lane_addr + kColO + half * 32, o);
+            tmem_ld_x32(o_addr, o);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&bars->o_free);    // the next item's first product may overwrite O now
-            // the two halves of the row sum meet through their own slots of the exchange buffer
-            xchg[(4 + half) * 128 + row] = l;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            l += xchg[(4 + (half ^ 1)) * 128 + row];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->o_free[grp]);    // the next item's first product may overwrite O now
+            float l_other;
+            ok = exchange(l, l_other);
+            PROF_FAIL(ok, 13, n);
+            if (!ok) break;
+            l += l_other;
             const float sink2 = p.sinks ? p.sinks[it.head] * 1.4426950408889634f : neg_inf_f();
             const float Mt = fmaxf(m, sink2);
             const float e = m == neg_inf_f() ? 0.f : ex2(m - Mt);
             const float total = l * e + (p.sinks ? ex2(sink2 - Mt) : 0.f);
             const float inv = total > 0.f ? e / total : 0.f;
-            if (it.q0 + row < it.t) {
-                uint16_t *out_row =
-                    p.out + (static_cast<size_t>(it.row0 + it.q0 + row) * p.heads + it.head) * kHeadDim + half * 32;
+            const int q_row = it.q0 + grp * kTileQ + row;
+            if (q_row < it.t) {
+                uint16_t *out_row = p.out + (static_cast<size_t>(it.row0 + q_row) * p.heads + it.head) * kHeadDim + half * 32;
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint4 v = make_uint4(pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
@@ -423,16 +645,12 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                     *reinterpret_cast<uint4 *>(out_row + i) = v;
                 }
             }
-            ++n_it;
+            PROF_END(6, t_epi);
         }
+        PROF_END(7, t_soft);
         if (!ok && lane == 0) raise_status(p.status, kStatusWaitTimeout);
-#ifdef CC_PREFILL_PROF
-        if (tid == 64) {
-            atomicAdd(&g_prefill_prof[8], static_cast<unsigned long long>(clock64() - soft_t0));
-            atomicAdd(&g_prefill_prof[9], static_cast<unsigned long long>(g));
-        }
-#endif
     }
+    PROF_FLUSH();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -444,6 +662,11 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
 }  // namespace
 
 #ifdef CC_PREFILL_PROF
+extern "C" void cc_debug_prefill_trace(long long *out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(long long) * 4 * 48 * 6);
+    cudaMemcpyFromSymbol(out + 4 * 48 * 6, g_prefill_trace2, sizeof(long long) * 3 * 96);
+}
 extern "C" void cc_debug_prefill_prof(unsigned long long *out, int reset) {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out, g_prefill_prof, sizeof(unsigned long long) * 16);
@@ -459,7 +682,7 @@ void launch_prefill(const PrefillParams &p, cudaStream_t stream) {
     int device = 0, sms = 148;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const long long items = static_cast<long long>(p.seqs) * ((p.max_t + kTileQ - 1) / kTileQ) * p.heads;
+    const long long items = static_cast<long long>(p.seqs) * ((p.max_t + 2 * kTileQ - 1) / (2 * kTileQ)) * p.heads;
     const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);   // one persistent CTA per SM
     prefill_kernel<<<grid, kThreadsPrefill, kPrefillSmem, stream>>>(p);
 }
