@@ -328,6 +328,36 @@ class DecodeBench:
         outs = [layer.out.view(np.uint16)[: n * h * D] for layer in self.layers]
         return int(outs[0][0]) + int(outs[1][0])  # touch the results on the host
 
+    def e2e_open(self):
+        """Records the step once, the way a decode loop does: the slices are fixed (this step's
+        positions and lengths go into row 0 of their buffers), and every later step only writes
+        its inputs into the host side of the buffers and replays the batch."""
+        n, h = self.seqs, self.heads
+        nb = len(self.layers[0].buffers())
+        self._replay = self.gpu.batch(self.all_buffers())
+        saved = self.len_all
+        self.len_all = np.broadcast_to(saved.max(axis=0, keepdims=True), saved.shape)  # split sizing: the longest step
+        for li, base in ((0, 0), (1, nb)):
+            self.record_step(self._replay, li, 0, base)
+            self._replay.read_back(self.compute.Slice(base + self.layers[li].OUT, 0, n * h * D * 2))
+        self._replay.end_recording()
+        self.len_all = saved
+
+    def e2e_replay(self, step):
+        n, h = self.seqs, self.heads
+        for layer in self.layers:
+            layer.q.write(self.q_host); layer.k.write(self.k_host); layer.v.write(self.v_host)
+            layer.positions.write(self.pos_all[step], offset=0)
+            layer.seq_lens.write(self.len_all[step], offset=0)
+        done = self._replay.replay()
+        if isinstance(done.gpu_time, Exception):
+            raise done.gpu_time
+        outs = [layer.out.view(np.uint16)[: n * h * D] for layer in self.layers]
+        return int(outs[0][0]) + int(outs[1][0])  # touch the results on the host
+
+    def e2e_close(self):
+        self._replay.drop()
+
     def e2e_bytes(self):
         n, h, g = self.seqs, self.heads, self.kv_heads
         h2d = 2 * (n * h * D * 2 + 2 * n * g * D * 2 + 2 * n * 4)
@@ -676,14 +706,16 @@ def run_gpu(args):
 
     # ---- end to end through host buffers ---------------------------------------------------
     base = total_steps + 1
+    bench.e2e_open()
     for i in range(args.warmup):
-        bench.e2e_step(base + i)
+        bench.e2e_replay(base + i)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        bench.e2e_step(base + args.warmup + i)
+        bench.e2e_replay(base + args.warmup + i)
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    bench.e2e_close()
     e2e_value = total_bytes * args.steps / e2e_s / 1e9
     h2d, d2h = bench.e2e_bytes()
 

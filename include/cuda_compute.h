@@ -350,11 +350,13 @@ typedef void (*cc_completion_fn)(void *user, int status, const char *message, do
 int cc_batch_commit(cc_batch *batch, cc_completion_fn done, void *user);
 /* Commit and wait on the calling thread. */
 int cc_batch_commit_wait(cc_batch *batch, double *gpu_seconds);
-/* Runs everything recorded so far and waits, keeping the batch: it can be replayed again (a
- * decode step records once and replays per token; the recorded slices and scalars are fixed, what
- * the host wrote into the buffers since the last run is uploaded first, read-backs are repeated).
- * Between replays the buffers are usable on the host like after a completion.  No counterpart in
- * metal-compute, which records every submission anew.  End with cc_batch_drop. */
+/* A batch that is recorded once and run many times (a decode step records once and replays per
+ * token).  cc_batch_end_recording closes the recording and hands the buffers back to the host;
+ * cc_batch_replay_wait then takes them, uploads what the host wrote since the last run, runs
+ * everything recorded (slices and scalars as recorded), repeats the read-backs, waits, and hands
+ * the buffers back again.  No counterpart in metal-compute, which records every submission anew
+ * (gpt-oss/src/gpu.rs:931-992).  End with cc_batch_drop. */
+int cc_batch_end_recording(cc_batch *batch);
 int cc_batch_replay_wait(cc_batch *batch, double *gpu_seconds);
 /* Dropping a batch (apple.rs:553-561): nothing recorded runs... see INTEGRATION notes: work
  * already enqueued is waited for, buffers are handed back, no callback. */

@@ -183,6 +183,7 @@ SYMBOLS = {
     "cc_batch_read_back": (c_int, [c_void_p, Slice]),
     "cc_batch_commit": (c_int, [c_void_p, COMPLETION_FN, c_void_p]),
     "cc_batch_commit_wait": (c_int, [c_void_p, POINTER(c_double)]),
+    "cc_batch_end_recording": (c_int, [c_void_p]),
     "cc_batch_replay_wait": (c_int, [c_void_p, POINTER(c_double)]),
     "cc_batch_drop": (None, [c_void_p]),
     "cc_batch_dispatches": (c_uint32, [c_void_p]),
@@ -467,6 +468,10 @@ class Batch:
         if code != 0:
             return Completed(self._buffers, _ERRORS.get(code, Error)(lib().cc_last_error().decode()))
         return Completed(self._buffers, seconds.value)
+
+    def end_recording(self) -> None:
+        """Closes the recording of a batch that will be replayed; the buffers are the host's again."""
+        check(lib().cc_batch_end_recording(self._h))
 
     def replay(self) -> Completed:
         """Runs what is recorded and waits, keeping the batch for further replays."""

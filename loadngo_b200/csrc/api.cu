@@ -431,6 +431,34 @@ const char *status_text(uint32_t s) {
     }
 }
 
+// Waits for a submitted job's end event; returns its status, message and GPU seconds, and hands
+// its buffers back.
+int finish(cc_gpu *gpu, Pending &job, std::string *message_out, double *seconds_out) {
+    int status = CC_OK;
+    std::string message = job.submit_error;
+    double seconds = 0.0;
+    cudaError_t e = cudaEventSynchronize(job.end);
+    if (e != cudaSuccess) {
+        status = CC_GPU;
+        message = std::string("batch failed: ") + cudaGetErrorString(e);
+    } else {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, job.begin, job.end) == cudaSuccess) seconds = ms * 1e-3;
+        if (!message.empty()) status = CC_GPU;
+        const uint32_t dev_status = *gpu->status_host;
+        if (dev_status != 0 && status == CC_OK) {
+            status = CC_GPU;
+            message = status_text(dev_status);
+        }
+    }
+    cudaEventDestroy(job.begin);
+    cudaEventDestroy(job.end);
+    for (cc_buffer *b : job.buffers) b->in_flight.store(false, std::memory_order_release);
+    *message_out = message;
+    *seconds_out = seconds;
+    return status;
+}
+
 void watcher_main(cc_gpu *gpu) {
     cudaSetDevice(gpu->device);
     for (;;) {
@@ -442,26 +470,9 @@ void watcher_main(cc_gpu *gpu) {
             gpu->queue.pop_front();
         }
         if (job.stop) return;
-        int status = CC_OK;
-        std::string message = job.submit_error;
+        std::string message;
         double seconds = 0.0;
-        cudaError_t e = cudaEventSynchronize(job.end);
-        if (e != cudaSuccess) {
-            status = CC_GPU;
-            message = std::string("batch failed: ") + cudaGetErrorString(e);
-        } else {
-            float ms = 0.f;
-            if (cudaEventElapsedTime(&ms, job.begin, job.end) == cudaSuccess) seconds = ms * 1e-3;
-            if (!message.empty()) status = CC_GPU;
-            const uint32_t dev_status = *gpu->status_host;
-            if (dev_status != 0 && status == CC_OK) {
-                status = CC_GPU;
-                message = status_text(dev_status);
-            }
-        }
-        cudaEventDestroy(job.begin);
-        cudaEventDestroy(job.end);
-        for (cc_buffer *b : job.buffers) b->in_flight.store(false, std::memory_order_release);
+        const int status = finish(gpu, job, &message, &seconds);
         if (job.done) job.done(job.user, status, message.c_str(), seconds);
         {
             std::lock_guard<std::mutex> lock(gpu->mu);
@@ -1103,7 +1114,7 @@ namespace {
 
 // Uploads what the host changed, runs the recorded work, copies requested ranges back, and
 // queues the completion.  Consumes the batch.
-int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false) {
+int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false, Pending *inline_job = nullptr) {
     cc_gpu *gpu = b->gpu;
     cudaSetDevice(gpu->device);
     if (keep)   // a replay takes its buffers again (they came back when the last run completed)
@@ -1148,6 +1159,10 @@ int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false) {
     cudaMemcpyAsync(gpu->status_host, gpu->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
     cudaMemsetAsync(gpu->status_dev, 0, sizeof(uint32_t), s);
     cudaEventRecord(job.end, s);
+    if (inline_job) {   // the caller waits on its own thread: no trip through the completion thread
+        *inline_job = std::move(job);
+        return CC_OK;
+    }
     {
         std::lock_guard<std::mutex> lock(gpu->mu);
         ++gpu->outstanding;
@@ -1195,18 +1210,26 @@ extern "C" int cc_batch_commit_wait(cc_batch *b, double *gpu_seconds) {
     return CC_OK;
 }
 
+extern "C" int cc_batch_end_recording(cc_batch *b) {
+    if (!b) return fail(CC_DISPATCH, "end recording: null batch");
+    for (cc_buffer *buf : b->buffers) buf->in_flight.store(false, std::memory_order_release);
+    b->replayed = true;
+    return CC_OK;
+}
+
 extern "C" int cc_batch_replay_wait(cc_batch *b, double *gpu_seconds) {
     if (!b) return fail(CC_DISPATCH, "replay: null batch");
-    for (cc_buffer *buf : b->buffers)
-        if (buf->in_flight.load(std::memory_order_acquire) && !b->replayed)
-            break;   // first run: the batch has owned its buffers since cc_batch_begin
-    b->replayed = true;
-    WaitBox box;
-    if (int rc = submit(b, wait_done, &box, true)) return rc;
-    std::unique_lock<std::mutex> lock(box.mu);
-    box.cv.wait(lock, [&] { return box.ready; });
-    if (gpu_seconds) *gpu_seconds = box.seconds;
-    if (box.status != CC_OK) return fail(static_cast<cc_status>(box.status), "%s", box.message.c_str());
+    if (!b->replayed) return fail(CC_DISPATCH, "replay: cc_batch_end_recording has not been called");
+    // Replays of one stream complete in order with everything queued before them, so the caller
+    // can wait for the end event itself; the completion thread (two thread hand-overs per run)
+    // stays out of the loop a decode step replays in.
+    Pending job;
+    if (int rc = submit(b, nullptr, nullptr, true, &job)) return rc;
+    std::string message;
+    double seconds = 0.0;
+    const int status = finish(b->gpu, job, &message, &seconds);
+    if (gpu_seconds) *gpu_seconds = seconds;
+    if (status != CC_OK) return fail(static_cast<cc_status>(status), "%s", message.c_str());
     return CC_OK;
 }
 

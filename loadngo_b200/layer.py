@@ -126,6 +126,36 @@ class PagedAttentionLayer:
             raise done.gpu_time
         return self.out.view(np.uint16)[: n * self.heads * HEAD_DIM].reshape(n, self.heads, HEAD_DIM).copy()
 
+    def open_decode_loop(self, n: int, max_seq_len: int) -> None:
+        """Records one decode step for sequences 0..n-1 (append, attend, read the output back)
+        to be replayed once per token by `decode_step_replayed`; `max_seq_len` bounds the length
+        any of the sequences reaches while the loop is open (it sizes the split of long caches)."""
+        self._loop_n = n
+        self._loop = self.gpu.batch(self.buffers())
+        self.record_append(self._loop, n)
+        self.record_decode(self._loop, n, max_seq_len)
+        self._loop.read_back(self._s(self.OUT, n * self.heads * HEAD_DIM * BF16))
+        self._loop.end_recording()
+
+    def decode_step_replayed(self, q: np.ndarray, k: np.ndarray, v: np.ndarray) -> np.ndarray:
+        """`decode_step` without recording anything: stage this token's inputs and replay."""
+        n = self._loop_n
+        seq_ids = np.arange(n)
+        positions = self.cache.lens[seq_ids].astype(np.int32)
+        for s_, p_ in zip(seq_ids, positions):
+            self.cache.reserve(int(s_), int(p_) + 1)
+        self.cache.flush_table()
+        self._stage(q, k, v, positions, seq_ids)
+        self.seq_lens.write((positions + 1).astype(np.int32))
+        done = self._loop.replay()
+        if isinstance(done.gpu_time, Exception):
+            raise done.gpu_time
+        return self.out.view(np.uint16)[: n * self.heads * HEAD_DIM].reshape(n, self.heads, HEAD_DIM).copy()
+
+    def close_decode_loop(self) -> None:
+        self._loop.drop()
+        self._loop = None
+
     def prefill(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, counts) -> np.ndarray:
         """`counts[s]` new positions for sequence s (rows of q, k, v back to back), appended at
         each sequence's next position, then attended causally."""

@@ -261,3 +261,32 @@ def test_bad_inputs_are_rejected_before_launch_or_reported_after(gpu):
     done = batch.run()
     assert isinstance(done.gpu_time, compute.GpuError)
     layer.free()
+
+
+def test_replayed_decode_loop_equals_fresh_batches(gpu):
+    """One recorded step replayed per token gives bit for bit what a freshly recorded batch per
+    token gives (same kernels, same inputs), and both match the oracle."""
+    rng = np.random.default_rng(41)
+    seqs, steps = 3, 24
+    sinks = rng.standard_normal(64).astype(np.float32)
+    make = lambda: PagedAttentionLayer(gpu, seqs=seqs, max_context=steps, max_new=seqs, window=16, sinks=sinks,
+                                       rng=np.random.default_rng(5))
+    fresh, looped = make(), make()
+    refs = [oracle.Session(64, 8, 64, steps, window=16, sinks=sinks, rope=oracle.Rope(), cache_bf16=True)
+            for _ in range(seqs)]
+    looped.open_decode_loop(seqs, steps)
+    for _ in range(steps):
+        q = oracle.round_bf16(rng.standard_normal((seqs, 64, 64)).astype(np.float32))
+        k = oracle.round_bf16(rng.standard_normal((seqs, 8, 64)).astype(np.float32))
+        v = oracle.round_bf16(rng.standard_normal((seqs, 8, 64)).astype(np.float32))
+        qb, kb, vb = oracle.f32_to_bf16_bits(q), oracle.f32_to_bf16_bits(k), oracle.f32_to_bf16_bits(v)
+        a = fresh.decode_step(qb, kb, vb)
+        b = looped.decode_step_replayed(qb, kb, vb)
+        assert np.array_equal(a, b)
+        got = oracle.bf16_bits_to_f32(b)
+        for s in range(seqs):
+            want, _ = refs[s].feed(q[s:s + 1], k[s:s + 1], v[s:s + 1])
+            assert np.abs(got[s] - want[0]).max() <= 1e-2
+    looped.close_decode_loop()
+    fresh.free()
+    looped.free()
