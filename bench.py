@@ -550,7 +550,7 @@ def run_block(args):
     (4096 -> 2880, row-parallel), NCCL all-reduce, residual.  Weights N(0, 0.02), hidden N(0,1),
     16 x 2048-token prefill then 128 decode steps."""
     from loadngo_b200 import compute
-    from loadngo_b200.block import HIDDEN, AttentionBlock, shard_weights
+    from loadngo_b200.block import HIDDEN, AttentionBlock, make_peer_group, shard_weights
     from oracle import oracle
     import ctypes
     torch, dist, world, rank, local = _dist_setup()
@@ -574,7 +574,7 @@ def run_block(args):
     sinks = rng.standard_normal(64).astype(np.float32)
     lq, lo = shard_weights(w_qkv, w_o, world, rank)
     kvl = KV_HEADS // world
-    block = AttentionBlock(gpu, seqs=seqs, max_context=T + decode_steps + 8, max_tokens=seqs * T,
+    block = AttentionBlock(gpu, seqs=seqs, max_context=T + 2 * decode_steps + 16, max_tokens=seqs * T,
                            w_qkv=oracle.f32_to_bf16_bits(lq), w_o=oracle.f32_to_bf16_bits(lo), norm=norm,
                            sinks=sinks[rank * kvl * GROUP:(rank + 1) * kvl * GROUP], kv_local=kvl, comm=comm)
     hidden = oracle.f32_to_bf16_bits(rng.standard_normal((seqs * T, HIDDEN)).astype(np.float32))
@@ -612,6 +612,31 @@ def run_block(args):
         decode_ms += ev[2].elapsed_time(ev[3])
     sync()
     decode_ms = _max_over_ranks(dist, world, decode_ms) / (decode_steps - 3)
+    h_library = block._read_h(seqs)
+
+    # the same decode steps with projection + exchange + residual as one kernel over peer memory
+    def gather(mine):
+        box = [None] * world
+        dist.all_gather_object(box, mine)
+        return box
+    group = make_peer_group(world, rank, seqs, gather if world > 1 else None)
+    block.peers = group
+    for _ in range(3):
+        block.decode(hd)
+    sync()
+    fused_ms = 0.0
+    for _ in range(decode_steps - 3):
+        plan = block.stage_decode(hd)
+        gpu.synchronize()
+        ev[2].record(stream)
+        block.launch(plan)
+        ev[3].record(stream)
+        gpu.synchronize()
+        fused_ms += ev[2].elapsed_time(ev[3])
+    sync()
+    fused_ms = _max_over_ranks(dist, world, fused_ms) / (decode_steps - 3)
+    h_fused = block._read_h(seqs)
+    finite = bool(np.isfinite(oracle.bf16_bits_to_f32(h_fused)).all())
     if rank == 0:
         m = seqs * T
         flops = 2 * m * 5120 * HIDDEN + 2 * m * HIDDEN * 4096 + 4 * D * 64 * (T * (T + 1) // 2) * seqs
@@ -620,9 +645,16 @@ def run_block(args):
                         "sink attention, O projection, NCCL all-reduce; 16 x 2048 prefill then 128 decode steps",
             "n_gpus": world, "prefill_ms": prefill_ms, "prefill_tflops_whole_job": flops / prefill_ms / 1e9,
             "prefill_tokens_per_s": m / prefill_ms * 1e3, "decode_ms_per_step": decode_ms,
-            "decode_tokens_per_s": seqs / decode_ms * 1e3, "all_reduce_bytes_prefill": m * HIDDEN * 2,
+            "decode_tokens_per_s": seqs / decode_ms * 1e3,
+            "decode_ms_per_step_fused": fused_ms, "decode_tokens_per_s_fused": seqs / fused_ms * 1e3,
+            "fused": "output projection + one-shot all-reduce over NVLink peer memory + residual add in one kernel "
+                     "(cc_oproj_reduce_residual_bf16); result finite: %s" % finite,
+            "all_reduce_bytes_prefill": m * HIDDEN * 2,
             "timed_with": "CUDA events on the launching stream around the block's kernels (inputs staged before), max over ranks",
             "collective": "ncclAllReduce bf16 sum" if world > 1 else "none (1 GPU)"}), flush=True)
+    if world > 1:
+        dist.barrier()   # nobody unmaps memory a peer's kernel may still write
+    L.cc_peer_group_free(group)
     if comm is not None:
         L.cc_comm_free(comm)
     if world > 1:

@@ -218,6 +218,24 @@ int cc_comm_init(const void *id128, int world, int rank, cc_comm **out);
 void cc_comm_free(cc_comm *comm);
 int cc_all_reduce_bf16(cc_comm *comm, void *stream, void *buffer, size_t count);
 
+/* The output projection, its sum over the ranks and the residual add as ONE kernel, for passes of
+ * a few rows (decode steps): h[rows][hidden] += sum over ranks of att_r[rows][k] . w_o_r[hidden][k]^T,
+ * all bf16 with f32 accumulation; the partial products cross NVLink as plain stores into the
+ * other ranks' memory (mapped with CUDA IPC) and are added in rank order, so every rank ends with
+ * the same bits.  Replaces cc_gemm_bf16 + cc_all_reduce_bf16 + cc_residual_add_bf16 there
+ * (model.rs:465-467, gpu.rs:807-817 in loadngo; the exchange has no counterpart in it).
+ * Set-up: every rank makes a group (one device allocation: flags and inboxes for `max_rows` rows),
+ * exports its 64-byte handle, the caller gathers the handles of all ranks in rank order, and every
+ * rank connects.  All ranks must call cc_oproj_reduce_residual_bf16 the same number of times with
+ * the same `rows`; waits on peers are bounded and end in the status word (CC_GPU at completion). */
+typedef struct cc_peer_group cc_peer_group;
+int cc_peer_group_new(int world, int rank, uint32_t max_rows, uint32_t hidden, cc_peer_group **out);
+int cc_peer_group_handle(cc_peer_group *group, void *handle64);
+int cc_peer_group_connect(cc_peer_group *group, const void *handles /* world x 64 bytes */);
+void cc_peer_group_free(cc_peer_group *group);
+int cc_oproj_reduce_residual_bf16(cc_peer_group *group, void *stream, const void *att, const void *w_o, void *h,
+                                  uint32_t rows, uint32_t k, uint32_t *status);
+
 /* ---- D. Gpu, Buffer, Resident -------------------------------------------------------------- */
 
 typedef struct cc_gpu cc_gpu;           /* metal-compute/src/apple.rs:72 `Gpu` */

@@ -36,14 +36,32 @@ def shard_weights(w_qkv: np.ndarray, w_o: np.ndarray, world: int, rank: int):
     return local_qkv, local_o
 
 
+def make_peer_group(world: int, rank: int, max_rows: int, gather=None) -> int:
+    """A connected cc_peer_group for the fused output projection.  `gather(handle_bytes)` returns
+    the 64-byte handles of all ranks in rank order (an all-gather by the caller's process group);
+    not needed for one rank."""
+    L = compute.lib()
+    g = ctypes.c_void_p()
+    compute.check(L.cc_peer_group_new(world, rank, max_rows, HIDDEN, ctypes.byref(g)))
+    if world > 1:
+        mine = (ctypes.c_ubyte * 64)()
+        compute.check(L.cc_peer_group_handle(g, mine))
+        handles = b"".join(gather(bytes(mine)))
+        assert len(handles) == 64 * world
+        compute.check(L.cc_peer_group_connect(g, handles))
+    return g.value
+
+
 class AttentionBlock:
     """bf16 attention block for `seqs` sequences on one rank.  `w_qkv`, `w_o` are this rank's
     shards as bfloat16 bit patterns (uint16), `norm` the RMSNorm weight (f32)."""
 
     def __init__(self, gpu: compute.Gpu, *, seqs: int, max_context: int, max_tokens: int, w_qkv: np.ndarray,
                  w_o: np.ndarray, norm: np.ndarray, sinks: np.ndarray, window: int = 0, kv_local: int = KV_HEADS,
-                 comm: int | None = None, eps: float = 1e-5, rng: np.random.Generator | None = None):
+                 comm: int | None = None, peers: int | None = None, eps: float = 1e-5,
+                 rng: np.random.Generator | None = None):
         self.gpu, self.kv_local, self.comm, self.eps = gpu, kv_local, comm, eps
+        self.peers = peers   # a connected cc_peer_group: decode passes fuse projection, exchange and residual
         self.heads = kv_local * GROUP
         self.qkv_width = (self.heads + 2 * kv_local) * HEAD_DIM
         self.att_width = self.heads * HEAD_DIM
@@ -101,6 +119,10 @@ class AttentionBlock:
                                     layer.q_offsets.device_ptr, layer.starts.device_ptr, seqs, n, max_t, sinks, heads,
                                     kvl, layer.window, layer.scale, layer.out.device_ptr, self.status.device_ptr)
             check(L.cc_attention_prefill_paged(s, ctypes.byref(a)))
+        if decode and self.peers is not None:
+            check(L.cc_oproj_reduce_residual_bf16(self.peers, s, layer.out.device_ptr, self.w_o.device_ptr,
+                                                  self.h.device_ptr, n, self.att_width, self.status.device_ptr))
+            return
         check(L.cc_gemm_bf16(self.blas, s, layer.out.device_ptr, self.w_o.device_ptr, self.o.device_ptr, n, HIDDEN,
                              self.att_width, self.att_width, self.att_width, HIDDEN))
         if self.comm is not None:

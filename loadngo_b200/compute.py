@@ -144,6 +144,12 @@ SYMBOLS = {
     "cc_comm_init": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
     "cc_comm_free": (None, [c_void_p]),
     "cc_all_reduce_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),
+    "cc_peer_group_new": (c_int, [c_int, c_int, c_uint32, c_uint32, POINTER(c_void_p)]),
+    "cc_peer_group_handle": (c_int, [c_void_p, c_void_p]),
+    "cc_peer_group_connect": (c_int, [c_void_p, c_void_p]),
+    "cc_peer_group_free": (None, [c_void_p]),
+    "cc_oproj_reduce_residual_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32,
+                                              c_void_p]),
     "cc_gpu_new": (c_int, [c_int, POINTER(c_void_p)]),
     "cc_gpu_free": (None, [c_void_p]),
     "cc_gpu_stream": (c_void_p, [c_void_p]),

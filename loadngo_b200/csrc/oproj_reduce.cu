@@ -1,0 +1,275 @@
+// Output projection, its sum over the ranks and the residual add of gpt-oss's attention block as
+// ONE kernel per decode step, with the exchange over NVLink peer memory instead of a library
+// all-reduce.
+//
+// Reference arithmetic: `o = layer.o.mul_vec(attended)`, `h += o` (gpt-oss/src/model.rs:465-467;
+// on the GPU path gemv/gemm + add_rows, gpt-oss/src/gpu.rs:807-817).  The reference runs on one
+// device and has no exchange; here W_o's columns are split over the ranks (one KV group each), so
+// every rank holds a partial product of every output element.
+//
+// Why one kernel: a decode step multiplies a handful of rows (one per sequence) by a 2880 x 512
+// slice of W_o: microseconds of work.  Behind it a library all-reduce of 92 KB costs its launch
+// and protocol latency (measured here at 8 ranks: ~100 us of a 187 us step).  In this kernel CTA j
+// of every rank owns the same 32 output columns: it multiplies (mma.sync, f32 accumulate, the inner
+// dimension split over its 8 warps), stores
+// its f32 partial tile straight into every rank's inbox (plain stores to peer memory mapped with
+// CUDA IPC), raises a flag per destination, waits for the flags of the same CTA on the other
+// ranks, adds the partials in rank order (every rank gets the same bits), adds the residual and
+// writes the bf16 residual stream.  No CTA waits for another CTA of its own GPU, and the grid
+// (90 CTAs) is always resident as a whole, so the only waits are on the peers, and they are
+// bounded: a wait that runs out raises the status word and the CTA returns.
+//
+// Inboxes are double-buffered by step parity: a rank cannot finish step s + 1 before every rank
+// has finished step s, so two buffers suffice.  Flags are step numbers and only ever grow.
+#include "../../include/cuda_compute.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int kColsPerCta = 32;      // four 8-column mma tiles
+constexpr int kRowsPerTile = 16;
+constexpr int kMaxWorld = 8;
+
+int fail(int code, const char *fmt, const char *arg = "") {
+    char text[320];
+    snprintf(text, sizeof text, fmt, arg);
+    return cc::set_error(code, text);
+}
+
+struct OprojParams {
+    const uint16_t *att;        // [rows][k] bf16: this rank's heads of the attention output
+    const uint16_t *w;          // [hidden][k] bf16: this rank's columns of W_o
+    uint16_t *h;                // [rows][hidden] bf16 residual stream (same on every rank)
+    float *inbox[kMaxWorld];    // every rank's inbox: [2 parities][world][max_rows][hidden] f32
+    uint32_t *flags[kMaxWorld]; // every rank's flags: [world][ctas]
+    uint32_t *status;
+    uint32_t rows, k, hidden, max_rows, world, rank, step;
+};
+
+__device__ __forceinline__ void store_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+constexpr int kWarps = 8;            // the inner dimension is split over the CTA's warps
+constexpr int kThreads = kWarps * 32;
+
+__global__ void __launch_bounds__(kThreads) oproj_reduce_kernel(const __grid_constant__ OprojParams p) {
+    __shared__ __align__(16) float part[kWarps][kRowsPerTile][kColsPerCta];   // each warp's share of the sum over k
+    __shared__ int failed;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int col0 = blockIdx.x * kColsPerCta;
+    const uint32_t parity = p.step & 1u;
+    const size_t plane = static_cast<size_t>(p.max_rows) * p.hidden;           // one rank's partial
+    const size_t my_slot = (static_cast<size_t>(parity) * p.world + p.rank) * plane;
+    if (tid == 0) failed = 0;
+
+    // ---- this rank's partial product, row tile by row tile, pushed to every rank's inbox.
+    // Warp w takes the 32-wide blocks w, w + 8, ... of the inner dimension for all 32 columns.
+    // A thread reads 16 contiguous bytes of a row per block (8 values) and feeds them to two
+    // mma.sync steps as the k pairs (2t, 2t+1), (2t+8, 2t+9): the order of k inside a block is
+    // permuted, identically for both operands, which a dot product does not notice.
+    const int g = lane >> 2, t = lane & 3;
+    for (uint32_t r0 = 0; r0 < p.rows; r0 += kRowsPerTile) {
+        float acc[4][4] = {};
+        const uint32_t ra = r0 + g, rb = ra + 8;
+        const bool va = ra < p.rows, vb = rb < p.rows;
+        const uint16_t *a_lo = p.att + static_cast<size_t>(va ? ra : 0) * p.k + t * 8;
+        const uint16_t *a_hi = p.att + static_cast<size_t>(vb ? rb : 0) * p.k + t * 8;
+        const uint16_t *w_row = p.w + static_cast<size_t>(col0 + g) * p.k + t * 8;
+#pragma unroll 2
+        for (uint32_t k0 = warp * 32; k0 < p.k; k0 += kWarps * 32) {
+            uint4 alo = *reinterpret_cast<const uint4 *>(a_lo + k0);
+            uint4 ahi = *reinterpret_cast<const uint4 *>(a_hi + k0);
+            if (!va) alo = make_uint4(0, 0, 0, 0);
+            if (!vb) ahi = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const uint4 b = *reinterpret_cast<const uint4 *>(w_row + static_cast<size_t>(nt) * 8 * p.k + k0);
+                cc::mma_bf16_16816(acc[nt], alo.x, ahi.x, alo.y, ahi.y, b.x, b.y);
+                cc::mma_bf16_16816(acc[nt], alo.z, ahi.z, alo.w, ahi.w, b.z, b.w);
+            }
+        }
+        __syncthreads();   // the buffers are free (the previous row tile's pushes are done)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int tc = nt * 8 + t * 2;
+            part[warp][g][tc] = acc[nt][0];
+            part[warp][g][tc + 1] = acc[nt][1];
+            part[warp][g + 8][tc] = acc[nt][2];
+            part[warp][g + 8][tc + 1] = acc[nt][3];
+        }
+        __syncthreads();
+        // 128 threads x 16 bytes = the 16 x 32 tile; rows are 128-byte runs in the inbox
+        const int pr = (tid & 127) >> 3, pc = (tid & 7) * 4;
+        if (tid < 128 && r0 + pr < p.rows) {
+            float4 v = *reinterpret_cast<const float4 *>(&part[0][pr][pc]);
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) {
+                const float4 u = *reinterpret_cast<const float4 *>(&part[w][pr][pc]);
+                v.x += u.x;
+                v.y += u.y;
+                v.z += u.z;
+                v.w += u.w;
+            }
+            const size_t at = my_slot + static_cast<size_t>(r0 + pr) * p.hidden + col0 + pc;
+            for (uint32_t d = 0; d < p.world; ++d) *reinterpret_cast<float4 *>(p.inbox[d] + at) = v;
+        }
+    }
+    // ---- tell every rank that this CTA's columns of this rank's partial are there
+    __threadfence_system();
+    __syncthreads();
+    if (tid < static_cast<int>(p.world))
+        store_release_sys(p.flags[tid] + static_cast<size_t>(p.rank) * gridDim.x + blockIdx.x, p.step);
+    // ---- wait for the same CTA of every rank (bounded), then sum in rank order
+    if (tid < static_cast<int>(p.world)) {
+        const uint32_t *flag = p.flags[p.rank] + static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
+        const long long began = clock64();
+        // flags are step numbers that only grow; the comparison survives wrap-around
+        while (static_cast<int32_t>(load_acquire_sys(flag) - p.step) < 0) {
+            if (clock64() - began > cc::kWaitCycles) {
+                atomicExch(&failed, 1);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (failed) {
+        if (tid == 0) cc::raise_status(p.status, cc::kStatusWaitTimeout);
+        return;
+    }
+    const float *mine = p.inbox[p.rank] + static_cast<size_t>(parity) * p.world * plane;
+    for (uint32_t r0 = 0; r0 < p.rows; r0 += kRowsPerTile) {
+        const int pr = (tid & 127) >> 3, pc = (tid & 7) * 4;
+        const uint32_t row = r0 + pr;
+        if (tid >= 128 || row >= p.rows) continue;
+        const size_t at = static_cast<size_t>(row) * p.hidden + col0 + pc;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s = 0; s < p.world; ++s) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(mine + s * plane + at));   // not through L1: peers wrote it
+            sum.x += v.x;
+            sum.y += v.y;
+            sum.z += v.z;
+            sum.w += v.w;
+        }
+        uint2 hv = *reinterpret_cast<const uint2 *>(p.h + at);
+        const float h0 = cc::bf16_bits_to_f32(static_cast<uint16_t>(hv.x)) + sum.x;
+        const float h1 = cc::bf16_bits_to_f32(static_cast<uint16_t>(hv.x >> 16)) + sum.y;
+        const float h2 = cc::bf16_bits_to_f32(static_cast<uint16_t>(hv.y)) + sum.z;
+        const float h3 = cc::bf16_bits_to_f32(static_cast<uint16_t>(hv.y >> 16)) + sum.w;
+        hv.x = cc::pack_bf16x2(h0, h1);
+        hv.y = cc::pack_bf16x2(h2, h3);
+        *reinterpret_cast<uint2 *>(p.h + at) = hv;
+    }
+}
+
+}  // namespace
+
+struct cc_peer_group {
+    int world = 1, rank = 0, device = 0;
+    uint32_t max_rows = 0, hidden = 0, ctas = 0, step = 0;
+    void *local = nullptr;                 // flags, then the inbox
+    size_t flag_bytes = 0, bytes = 0;
+    std::vector<void *> mapped;            // peers' allocations as opened here (null for this rank)
+    bool connected = false;
+};
+
+extern "C" int cc_peer_group_new(int world, int rank, uint32_t max_rows, uint32_t hidden, cc_peer_group **out) {
+    if (!out || world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+        return fail(CC_DISPATCH, "peer group: 1 to 8 ranks, rank inside");
+    if (max_rows == 0 || hidden == 0 || hidden % kColsPerCta != 0)
+        return fail(CC_DISPATCH, "peer group: rows > 0 and a width that is a multiple of 32");
+    cc_peer_group *g = new cc_peer_group;
+    g->world = world;
+    g->rank = rank;
+    g->max_rows = max_rows;
+    g->hidden = hidden;
+    g->ctas = hidden / kColsPerCta;
+    cudaGetDevice(&g->device);
+    g->flag_bytes = (static_cast<size_t>(world) * g->ctas * sizeof(uint32_t) + 255) & ~static_cast<size_t>(255);
+    g->bytes = g->flag_bytes + 2ull * world * max_rows * hidden * sizeof(float);
+    if (cudaMalloc(&g->local, g->bytes) != cudaSuccess) {
+        delete g;
+        return fail(CC_ALLOC, "peer group: device allocation failed");
+    }
+    cudaMemset(g->local, 0, g->bytes);
+    cudaDeviceSynchronize();
+    g->mapped.assign(world, nullptr);
+    g->connected = world == 1;
+    *out = g;
+    return CC_OK;
+}
+
+extern "C" int cc_peer_group_handle(cc_peer_group *g, void *handle64) {
+    if (!g || !handle64) return fail(CC_DISPATCH, "peer group: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, g->local);
+    if (e != cudaSuccess) return fail(CC_GPU, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    memcpy(handle64, &h, sizeof h);
+    return CC_OK;
+}
+
+extern "C" int cc_peer_group_connect(cc_peer_group *g, const void *handles) {
+    if (!g || !handles) return fail(CC_DISPATCH, "peer group: null argument");
+    cudaSetDevice(g->device);
+    for (int r = 0; r < g->world; ++r) {
+        if (r == g->rank || g->mapped[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const uint8_t *>(handles) + 64 * r, sizeof h);
+        const cudaError_t e = cudaIpcOpenMemHandle(&g->mapped[r], h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return fail(CC_GPU, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    }
+    g->connected = true;
+    return CC_OK;
+}
+
+extern "C" void cc_peer_group_free(cc_peer_group *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    for (void *m : g->mapped)
+        if (m) cudaIpcCloseMemHandle(m);
+    if (g->local) cudaFree(g->local);
+    delete g;
+}
+
+extern "C" int cc_oproj_reduce_residual_bf16(cc_peer_group *g, void *stream, const void *att, const void *w_o, void *h,
+                                             uint32_t rows, uint32_t k, uint32_t *status) {
+    if (!g || !att || !w_o || !h) return fail(CC_DISPATCH, "oproj_reduce: null argument");
+    if (!g->connected) return fail(CC_DISPATCH, "oproj_reduce: the peer group is not connected");
+    if (rows == 0 || rows > g->max_rows) return fail(CC_DISPATCH, "oproj_reduce: rows outside the group's inbox");
+    if (k == 0 || k % 32 != 0) return fail(CC_DISPATCH, "oproj_reduce: the inner width must be a multiple of 32");
+    if (reinterpret_cast<uintptr_t>(att) % 16 || reinterpret_cast<uintptr_t>(w_o) % 16 || reinterpret_cast<uintptr_t>(h) % 8)
+        return fail(CC_DISPATCH, "oproj_reduce: misaligned pointer");
+    OprojParams p{};
+    p.att = static_cast<const uint16_t *>(att);
+    p.w = static_cast<const uint16_t *>(w_o);
+    p.h = static_cast<uint16_t *>(h);
+    for (int r = 0; r < g->world; ++r) {
+        uint8_t *base = static_cast<uint8_t *>(r == g->rank ? g->local : g->mapped[r]);
+        p.flags[r] = reinterpret_cast<uint32_t *>(base);
+        p.inbox[r] = reinterpret_cast<float *>(base + g->flag_bytes);
+    }
+    p.status = status;
+    p.rows = rows;
+    p.k = k;
+    p.hidden = g->hidden;
+    p.max_rows = g->max_rows;
+    p.world = static_cast<uint32_t>(g->world);
+    p.rank = static_cast<uint32_t>(g->rank);
+    p.step = ++g->step;
+    oproj_reduce_kernel<<<g->ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return cudaGetLastError() == cudaSuccess ? CC_OK : fail(CC_GPU, "oproj_reduce launch failed");
+}

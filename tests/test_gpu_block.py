@@ -93,3 +93,121 @@ def test_split_by_kv_group_sums_to_the_unsplit_block(gpu):
     err, cos = helpers.errors(total, want)
     print(f"\nsum of 4 shards vs unsplit output projection: max_abs={err:.4f} cos={cos:.6f}")
     assert err <= 3e-2 and cos >= 0.9999
+
+
+def test_fused_output_projection_on_one_rank(gpu):
+    """Decode steps with the output projection, the (here single-rank) exchange and the residual
+    add as one kernel, against the oracle and against the three-call path on the same inputs."""
+    from loadngo_b200.block import make_peer_group
+    rng = np.random.default_rng(47)
+    w_qkv, w_o, norm, sinks = make_weights(rng)
+    seqs = 5
+    ref = OracleBlock(w_qkv, w_o, norm, sinks, seqs, 64, 0)
+    args = dict(seqs=seqs, max_context=64, max_tokens=seqs, w_qkv=oracle.f32_to_bf16_bits(w_qkv),
+                w_o=oracle.f32_to_bf16_bits(w_o), norm=norm, sinks=sinks)
+    plain = AttentionBlock(gpu, rng=np.random.default_rng(1), **args)
+    group = make_peer_group(1, 0, seqs)
+    fused = AttentionBlock(gpu, rng=np.random.default_rng(1), peers=group, **args)
+    for step in range(20):
+        hd = oracle.round_bf16(rng.standard_normal((seqs, HIDDEN)).astype(np.float32))
+        a = oracle.bf16_bits_to_f32(plain.decode(oracle.f32_to_bf16_bits(hd)))
+        b = oracle.bf16_bits_to_f32(fused.decode(oracle.f32_to_bf16_bits(hd)))
+        want = np.concatenate([ref.feed(s, hd[s:s + 1]) for s in range(seqs)])
+        err, cos = helpers.errors(b, want)
+        assert err <= 6e-2 and cos >= 0.9995, f"step {step}: {err} {cos}"
+        # the fused kernel keeps the product in f32 until the residual add; the three-call path
+        # rounds it to bf16 first: they differ by that rounding only
+        assert np.abs(a - b).max() <= 4e-2
+    plain.free()
+    fused.free()
+    compute.lib().cc_peer_group_free(group)
+
+
+def _two_rank_child(rank, world, pipes, result):
+    """One rank of the two-GPU test: its shard of the block on GPU `rank`, decode steps with the
+    fused output projection; handles of the peer groups travel through `pipes`."""
+    import numpy as np
+    from loadngo_b200 import compute
+    from loadngo_b200.block import HIDDEN, AttentionBlock, make_peer_group, shard_weights
+    from oracle import oracle
+    gpu = compute.Gpu(rank)
+    rng = np.random.default_rng(53)   # same weights and inputs on both ranks
+    w_qkv, w_o, norm, sinks = make_weights(rng)
+    lq, lo = shard_weights(w_qkv, w_o, world, rank)
+    kvl = 8 // world
+    seqs = 4
+
+    def gather(mine):
+        for r in range(world):
+            if r != rank:
+                pipes[rank][r].send(mine)
+        got = [None] * world
+        got[rank] = mine
+        for r in range(world):
+            if r != rank:
+                got[r] = pipes[r][rank].recv()
+        return got
+
+    group = make_peer_group(world, rank, seqs, gather)
+    block = AttentionBlock(gpu, seqs=seqs, max_context=64, max_tokens=seqs, w_qkv=oracle.f32_to_bf16_bits(lq),
+                           w_o=oracle.f32_to_bf16_bits(lo), norm=norm, sinks=sinks[rank * kvl * 8:(rank + 1) * kvl * 8],
+                           kv_local=kvl, peers=group, rng=np.random.default_rng(2))
+    outs = []
+    for _ in range(12):
+        hd = oracle.round_bf16(rng.standard_normal((seqs, HIDDEN)).astype(np.float32))
+        outs.append(block.decode(oracle.f32_to_bf16_bits(hd)))
+    result.put((rank, np.stack(outs)))
+    # leave only after the peer has finished too: its kernels still read and write this rank's memory
+    for r in range(world):
+        if r != rank:
+            pipes[rank][r].send(b"done")
+    for r in range(world):
+        if r != rank:
+            pipes[r][rank].recv()
+    block.free()
+    compute.lib().cc_peer_group_free(group)
+
+
+def test_fused_output_projection_across_two_gpus(gpu):
+    """Two processes, one GPU each, partial products exchanged through peer memory: both ranks end
+    with the same bits, and they match the unsplit block within the rounding of the split."""
+    import multiprocessing as mp
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    world = 2
+    pipes = [[None] * world for _ in range(world)]
+    ends = [[None] * world for _ in range(world)]
+    for a in range(world):
+        for b in range(world):
+            if a != b:
+                ends[a][b], pipes[a][b] = ctx.Pipe(duplex=False)   # pipes[a][b]: a sends; ends[a][b]: b receives
+    # a child needs, per peer, the sending end of its own pipe and the receiving end of the peer's
+    result = ctx.Queue()
+    procs = []
+    for rank in range(world):
+        view = [[None] * world for _ in range(world)]
+        for r in range(world):
+            if r != rank:
+                view[rank][r] = pipes[rank][r]
+                view[r][rank] = ends[r][rank]
+        p = ctx.Process(target=_two_rank_child, args=(rank, world, view, result))
+        p.start()
+        procs.append(p)
+    got = dict(result.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert np.array_equal(got[0], got[1])
+    # the unsplit block on this process's GPU, same inputs
+    rng = np.random.default_rng(53)
+    w_qkv, w_o, norm, sinks = make_weights(rng)
+    whole = AttentionBlock(gpu, seqs=4, max_context=64, max_tokens=4, w_qkv=oracle.f32_to_bf16_bits(w_qkv),
+                           w_o=oracle.f32_to_bf16_bits(w_o), norm=norm, sinks=sinks, rng=np.random.default_rng(2))
+    for step in range(12):
+        hd = oracle.round_bf16(rng.standard_normal((4, HIDDEN)).astype(np.float32))
+        want = oracle.bf16_bits_to_f32(whole.decode(oracle.f32_to_bf16_bits(hd)))
+        err, cos = helpers.errors(oracle.bf16_bits_to_f32(got[0][step]), want)
+        assert err <= 4e-2 and cos >= 0.9999, f"step {step}: {err} {cos}"
+    whole.free()
