@@ -318,6 +318,18 @@ int cc_batch_copy_rows(cc_batch *batch, cc_slice src, uint64_t src_stride, cc_sl
 /* Batch::rmsnorm_rows (apple.rs:1733-1758): v = w * v / sqrt(mean(v^2) + eps) in place. */
 int cc_batch_rmsnorm_rows(cc_batch *batch, cc_slice v, cc_slice w, uint64_t rows, uint64_t d, uint64_t stride,
                           float eps);
+/* Batch::gemv_q8_0, gemm_q8_0, gemm_q8_0_tiled (apple.rs:1812-1882): y[p] = W x[p] for a
+ * rows x cols matrix in repacked ggml Q8_0 (`codes`: every row's signed bytes in order; `scales`:
+ * one binary16 per 32 of them, weights/src/q8_0.rs:17-31); x: n rows of cols floats x_stride
+ * apart (a multiple of 4), y: n rows of `rows` floats y_stride apart.  Needs cols % 32 == 0,
+ * codes and x on 16-byte boundaries; the tiled form also rows % 64 == 0 and n % 32 == 0 (the
+ * reference's padding rule; one kernel serves all three here). */
+int cc_batch_gemv_q8_0(cc_batch *batch, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                       uint64_t cols);
+int cc_batch_gemm_q8_0(cc_batch *batch, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                       uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride);
+int cc_batch_gemm_q8_0_tiled(cc_batch *batch, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                             uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride);
 /* Batch::add_rows (apple.rs:1886-1911): dst[r] += src[r * src_stride ..]; stride 0 = a bias. */
 int cc_batch_add_rows(cc_batch *batch, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
                       uint64_t width);

@@ -173,6 +173,11 @@ SYMBOLS = {
     "cc_batch_copy_rows": (c_int, [c_void_p, Slice, c_uint64, Slice, c_uint64, c_uint64, c_uint64]),
     "cc_batch_rmsnorm_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64, c_float]),
     "cc_batch_add_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_gemv_q8_0": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64]),
+    "cc_batch_gemm_q8_0": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64, c_uint64,
+                                   c_uint64]),
+    "cc_batch_gemm_q8_0_tiled": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64, c_uint64,
+                                         c_uint64]),
     "cc_batch_rotate_halves": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64]),
     "cc_batch_attention_grouped": (c_int, [c_void_p, Slice, Slice, Slice, POINTER(Slice), Slice,
                                            POINTER(_GroupedShape)]),
@@ -404,6 +409,19 @@ class Batch:
     def add_rows(self, dst: Slice, src, rows: int, width: int) -> None:
         s, ss = src
         check(lib().cc_batch_add_rows(self._h, dst, s, ss, rows, width))
+
+    def gemv_q8_0(self, matrix, x: Slice, y: Slice, rows: int, cols: int) -> None:
+        """`Batch::gemv_q8_0` (apple.rs:1812-1830); `matrix` = (codes, scales)."""
+        codes, scales = matrix
+        check(lib().cc_batch_gemv_q8_0(self._h, codes, scales, x, y, rows, cols))
+
+    def gemm_q8_0(self, matrix, x: Slice, y: Slice, rows: int, cols: int, n: int, strides) -> None:
+        codes, scales = matrix
+        check(lib().cc_batch_gemm_q8_0(self._h, codes, scales, x, y, rows, cols, n, strides[0], strides[1]))
+
+    def gemm_q8_0_tiled(self, matrix, x: Slice, y: Slice, rows: int, cols: int, n: int, strides) -> None:
+        codes, scales = matrix
+        check(lib().cc_batch_gemm_q8_0_tiled(self._h, codes, scales, x, y, rows, cols, n, strides[0], strides[1]))
 
     def rotate_halves(self, x: Slice, table: Slice, rows: int, heads_dim) -> None:
         heads, dim = heads_dim

@@ -682,6 +682,11 @@ struct cc_batch {
     std::vector<cc_slice> outputs;  // ranges the recorded work writes; marked device-newer at commit
     uint32_t dispatches = 0;
     bool replayed = false;
+    // A replayed batch runs its kernels as one CUDA graph from the second replay on (captured
+    // during the first): a decode step is a handful of short kernels, and launching them one by
+    // one costs more than they run.
+    cudaGraphExec_t graph = nullptr;
+    bool graph_tried = false;
 };
 
 namespace {
@@ -815,6 +820,59 @@ extern "C" int cc_batch_rmsnorm_rows(cc_batch *b, cc_slice v, cc_slice w, uint64
     wrote(b, v);
     ++b->dispatches;
     return CC_OK;
+}
+
+namespace {
+
+// The three Q8_0 products share their checks (Batch::check_q8_0, gemm_args: apple.rs:1796-1806,
+// 987-1013) and their kernel.
+int record_q8_0(cc_batch *b, const char *what, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride) {
+    if (!b) return fail(CC_DISPATCH, "%s: null batch", what);
+    if (rows == 0 || cols == 0) return fail(CC_DISPATCH, "%s: empty matrix", what);
+    if (cols % 32 != 0) return fail(CC_DISPATCH, "Q8_0 rows of %llu are not whole blocks", (unsigned long long)cols);
+    if (n == 0 || x_stride < cols || y_stride < rows || x_stride % 4 != 0)
+        return fail(CC_DISPATCH, "%llu positions of %llu x %llu with strides %llu/%llu", (unsigned long long)n,
+                    (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)x_stride,
+                    (unsigned long long)y_stride);
+    uint32_t r, c, nn, xs, ys, tmp;
+    if (narrow(rows, &r) || narrow(cols, &c) || narrow(n, &nn) || narrow(x_stride, &xs) || narrow(y_stride, &ys) ||
+        narrow(rows * cols, &tmp))
+        return CC_DISPATCH;
+    uint8_t *pc, *ps, *px, *py;
+    if (int rc = check(b, "codes", codes, rows * cols, 16, &pc)) return rc;
+    if (int rc = check(b, "scales", scales, rows * cols / 32 * 2, 2, &ps)) return rc;
+    if (int rc = check(b, "x", x, ((n - 1) * x_stride + cols) * 4, 16, &px)) return rc;
+    if (int rc = check(b, "y", y, ((n - 1) * y_stride + rows) * 4, 4, &py)) return rc;
+    if (int rc = check_output(b, y, {&codes, &scales, &x})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_q8_0(reinterpret_cast<const int8_t *>(pc), ps, reinterpret_cast<const float *>(px),
+                        reinterpret_cast<float *>(py), r, c, nn, xs, ys, s);
+        return CC_OK;
+    });
+    wrote(b, y);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+}  // namespace
+
+extern "C" int cc_batch_gemv_q8_0(cc_batch *b, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                                  uint64_t cols) {
+    return record_q8_0(b, "gemv_q8_0", codes, scales, x, y, rows, cols, 1, cols, rows);
+}
+
+extern "C" int cc_batch_gemm_q8_0(cc_batch *b, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                                  uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride) {
+    return record_q8_0(b, "gemm_q8_0", codes, scales, x, y, rows, cols, n, x_stride, y_stride);
+}
+
+extern "C" int cc_batch_gemm_q8_0_tiled(cc_batch *b, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y,
+                                        uint64_t rows, uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride) {
+    if (rows % 64 != 0 || cols % 32 != 0 || n % 32 != 0)
+        return fail(CC_DISPATCH, "tiled Q8_0 product needs rows %% 64, cols %% 32 and n %% 32 == 0: %llu x %llu, n %llu",
+                    (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)n);
+    return record_q8_0(b, "gemm_q8_0_tiled", codes, scales, x, y, rows, cols, n, x_stride, y_stride);
 }
 
 extern "C" int cc_batch_add_rows(cc_batch *b, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
@@ -1143,10 +1201,39 @@ int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false, Pe
         mark(buf->dev_dirty_lo, buf->dev_dirty_hi, o.offset, o.offset + o.len);
     }
     cudaEventRecord(job.begin, s);
-    for (auto &fn : b->work) {
-        if (fn(s) != CC_OK) {
-            job.submit_error = g_error;
-            break;
+    if (keep && b->graph) {
+        if (cudaGraphLaunch(b->graph, s) != cudaSuccess) job.submit_error = "graph launch failed";
+    } else {
+        const bool capture = keep && b->replayed && !b->graph_tried && !b->work.empty();
+        bool capturing = false;
+        if (capture) {
+            b->graph_tried = true;
+            capturing = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        }
+        for (auto &fn : b->work) {
+            if (fn(s) != CC_OK) {
+                job.submit_error = g_error;
+                break;
+            }
+        }
+        if (capturing) {
+            cudaGraph_t graph = nullptr;
+            if (cudaStreamEndCapture(s, &graph) == cudaSuccess && graph && job.submit_error.empty()) {
+                if (cudaGraphInstantiate(&b->graph, graph, 0) != cudaSuccess) b->graph = nullptr;
+            } else {
+                cudaGetLastError();   // a kernel that cannot be captured: this batch stays on plain launches
+            }
+            if (graph) cudaGraphDestroy(graph);
+            if (b->graph) {
+                if (cudaGraphLaunch(b->graph, s) != cudaSuccess) job.submit_error = "graph launch failed";
+            } else if (job.submit_error.empty()) {
+                for (auto &fn : b->work) {   // nothing ran during the failed capture: run it now
+                    if (fn(s) != CC_OK) {
+                        job.submit_error = g_error;
+                        break;
+                    }
+                }
+            }
         }
     }
     for (const cc_slice &rb : b->read_backs) {
@@ -1237,5 +1324,6 @@ extern "C" void cc_batch_drop(cc_batch *b) {
     if (!b) return;
     // Nothing recorded has been launched: a dropped batch never runs (apple.rs:553-561).
     for (cc_buffer *buf : b->buffers) buf->in_flight.store(false, std::memory_order_release);
+    if (b->graph) cudaGraphExecDestroy(b->graph);
     delete b;
 }

@@ -25,4 +25,8 @@ void launch_rotate_halves(float *x, const float *table, uint32_t rows, uint32_t 
 void launch_attention_grouped(const float *q, const float *k, const float *v, float *out, const float *sinks,
                               const GroupedArgs &a, cudaStream_t stream);
 
+// y[p][r] = sum over c of scales[(r * cols + c) / 32] * codes[r * cols + c] * x[p][c] (q8_0.cu).
+void launch_q8_0(const int8_t *codes, const void *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
+                 uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream);
+
 }  // namespace cc

@@ -1,0 +1,170 @@
+// Products with ggml Q8_0 matrices: the Q/K/V/O projections of gpt-oss as shipped in its GGUF.
+//
+// Replaces `gemv_q8_0`, `gemm_q8_0` and `gemm_q8_0_tiled` (metal-compute/src/kernels.metal:1447-1638,
+// host entries metal-compute/src/apple.rs:1812-1882) with the same operands: `codes` holds every
+// row's signed bytes in order, `scales` one binary16 per 32 of them (the repacked layout of
+// weights/src/q8_0.rs:17-31); element c of row r is scales[(r * cols + c) / 32] * codes[r * cols + c].
+// x and y are float32, as in the reference, and so is the arithmetic: per block the products are
+// summed and scaled once (weights/src/q8_0.rs:102-131), float32 fused multiply-adds on the CUDA
+// cores.  The reference's own test holds these products to a relative error of 1e-5
+// (metal-compute/tests/q8_0_and_gpt_oss_glue.rs:139-160), which rules out bf16 or tf32 tensor-core
+// operands for x.
+//
+// One kernel serves all three entries.  A warp owns two rows of the matrix and walks their codes
+// 512 columns at a time, 16 bytes per lane (a block of 32 codes is two lanes' worth, so a lane's
+// 16 products share one scale); the x rows of up to kPos positions are staged in shared memory
+// per 512-column chunk and read as float4 by all warps of the CTA, so a matrix row is read from
+// HBM once per kPos positions.  With one position (a decode step) the kernel streams the matrix
+// once: it is HBM-bound, rows * cols bytes.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "legacy.cuh"
+
+namespace cc {
+namespace {
+
+constexpr int kChunk = 512;          // columns per step: 32 lanes x 16 codes
+constexpr int kRowsPerWarp = 2;
+constexpr int kWarpsQ8 = 8;
+
+template <int kPos>
+__global__ void __launch_bounds__(kWarpsQ8 * 32) q8_0_kernel(const int8_t *__restrict__ codes,
+                                                             const __half *__restrict__ scales,
+                                                             const float *__restrict__ x, float *__restrict__ y,
+                                                             uint32_t rows, uint32_t cols, uint32_t n,
+                                                             uint32_t x_stride, uint32_t y_stride) {
+    __shared__ __align__(16) float xs[kPos][kChunk];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row0 = (blockIdx.x * kWarpsQ8 + warp) * kRowsPerWarp;
+    const uint32_t p0 = blockIdx.y * kPos;
+    const uint32_t np = min(static_cast<uint32_t>(kPos), n - p0);
+    float acc[kRowsPerWarp][kPos];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r)
+#pragma unroll
+        for (int p = 0; p < kPos; ++p) acc[r][p] = 0.f;
+
+    for (uint32_t c0 = 0; c0 < cols; c0 += kChunk) {
+        const uint32_t width = min(static_cast<uint32_t>(kChunk), cols - c0);   // a multiple of 32
+        __syncthreads();
+        for (uint32_t i = threadIdx.x * 4; i < kPos * kChunk; i += kWarpsQ8 * 32 * 4) {
+            const uint32_t p = i / kChunk, c = i % kChunk;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p < np && c < width) v = *reinterpret_cast<const float4 *>(x + static_cast<size_t>(p0 + p) * x_stride + c0 + c);
+            *reinterpret_cast<float4 *>(&xs[p][c]) = v;
+        }
+        __syncthreads();
+        const uint32_t c = lane * 16;
+        if (c >= width) continue;
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const uint32_t row = row0 + r;
+            if (row >= rows) break;
+            const size_t at = static_cast<size_t>(row) * cols + c0 + c;
+            const int4 q = *reinterpret_cast<const int4 *>(codes + at);
+            const float d = __half2float(scales[at / 32]);
+            float w[16];
+            const int words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[4 * j] = static_cast<float>(static_cast<int8_t>(words[j]));
+                w[4 * j + 1] = static_cast<float>(static_cast<int8_t>(words[j] >> 8));
+                w[4 * j + 2] = static_cast<float>(static_cast<int8_t>(words[j] >> 16));
+                w[4 * j + 3] = static_cast<float>(static_cast<int8_t>(words[j] >> 24));
+            }
+#pragma unroll
+            for (int p = 0; p < kPos; ++p) {
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 v = *reinterpret_cast<const float4 *>(&xs[p][c + 4 * j]);
+                    sum = fmaf(w[4 * j], v.x, sum);
+                    sum = fmaf(w[4 * j + 1], v.y, sum);
+                    sum = fmaf(w[4 * j + 2], v.z, sum);
+                    sum = fmaf(w[4 * j + 3], v.w, sum);
+                }
+                acc[r][p] = fmaf(d, sum, acc[r][p]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r)
+#pragma unroll
+        for (int p = 0; p < kPos; ++p) {
+            float v = acc[r][p];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && row0 + r < rows && static_cast<uint32_t>(p) < np)
+                y[static_cast<size_t>(p0 + p) * y_stride + row0 + r] = v;
+        }
+}
+
+// One position (a decode step): the matrix is streamed once and nothing else matters.  A warp
+// owns one row and issues kUnroll 16-byte loads of codes per lane before it uses any (a whole
+// 2880- or 4096-wide row in one or two trips), so a launch costs about one HBM latency; x is read
+// through L1.
+template <int kUnroll>
+__global__ void __launch_bounds__(kWarpsQ8 * 32) q8_0_gemv_kernel(const int8_t *__restrict__ codes,
+                                                                  const __half *__restrict__ scales,
+                                                                  const float *__restrict__ x, float *__restrict__ y,
+                                                                  uint32_t rows, uint32_t cols) {
+    const float *xv = x;   // 12-16 KB read by every warp: it lives in L1
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * kWarpsQ8 + warp;
+    if (row >= rows) return;
+    const int8_t *rc = codes + static_cast<size_t>(row) * cols;
+    const __half *rs = scales + static_cast<size_t>(row) * (cols / 32);
+    float acc = 0.f;
+    for (uint32_t c0 = lane * 16; c0 < cols; c0 += kChunk * kUnroll) {
+        int4 q[kUnroll];
+        float d[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t c = c0 + u * kChunk;
+            const bool in = c < cols;
+            q[u] = in ? *reinterpret_cast<const int4 *>(rc + c) : make_int4(0, 0, 0, 0);
+            d[u] = in ? __half2float(rs[c / 32]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t c = min(c0 + u * kChunk, cols - 16);
+            const int words[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(xv + c + 4 * j));
+                sum = fmaf(static_cast<float>(static_cast<int8_t>(words[j])), v.x, sum);
+                sum = fmaf(static_cast<float>(static_cast<int8_t>(words[j] >> 8)), v.y, sum);
+                sum = fmaf(static_cast<float>(static_cast<int8_t>(words[j] >> 16)), v.z, sum);
+                sum = fmaf(static_cast<float>(static_cast<int8_t>(words[j] >> 24)), v.w, sum);
+            }
+            acc = fmaf(d[u], sum, acc);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[row] = acc;
+}
+
+}  // namespace
+
+void launch_q8_0(const int8_t *codes, const void *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
+                 uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream) {
+    const unsigned row_blocks = (rows + kWarpsQ8 * kRowsPerWarp - 1) / (kWarpsQ8 * kRowsPerWarp);
+    const __half *sc = static_cast<const __half *>(scales);
+    if (n == 1) {
+        if (cols <= 6 * kChunk)
+            q8_0_gemv_kernel<6><<<(rows + kWarpsQ8 - 1) / kWarpsQ8, kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols);
+        else
+            q8_0_gemv_kernel<8><<<(rows + kWarpsQ8 - 1) / kWarpsQ8, kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols);
+    } else if (n <= 4) {
+        q8_0_kernel<4><<<dim3(row_blocks, 1), kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols, n, x_stride, y_stride);
+    } else {
+        q8_0_kernel<8><<<dim3(row_blocks, (n + 7) / 8), kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols, n, x_stride,
+                                                                                 y_stride);
+    }
+}
+
+}  // namespace cc

@@ -270,3 +270,51 @@ void oracle_xorshift_values(uint64_t seed, long n, float *out) {
         out[i] = (float)(s >> 40) / (float)(1ull << 23) - 1.0f;
     }
 }
+
+/* ---- Q8_0 products (the projections as shipped in the GGUF) ---------------------------- */
+
+static float oracle_f16_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else { /* subnormal: normalise */
+            int e = -1;
+            do { ++e; man <<= 1; } while ((man & 0x400u) == 0);
+            bits = sign | (uint32_t)(127 - 15 - e) << 23 | (man & 0x3ffu) << 13;
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | man << 13;
+    } else {
+        bits = sign | (exp + 127 - 15) << 23 | man << 13;
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* y[r] = row r . x for a row-major matrix of ggml Q8_0 blocks (34 bytes: binary16 scale d, then
+ * 32 signed bytes q; element i is d * q[i]): per block the products are summed in f32 and
+ * scaled once, blocks in order (weights/src/q8_0.rs:102-131, `Q8Matrix::mul_rows`). */
+void oracle_q8_0_mul_vec(const uint8_t *blocks, long rows, long cols, const float *x, float *y) {
+    const long per_row = cols / 32;
+    for (long r = 0; r < rows; ++r) {
+        float acc = 0.0f;
+        for (long b = 0; b < per_row; ++b) {
+            const uint8_t *block = blocks + (r * per_row + b) * 34;
+            const float d = oracle_f16_to_f32((uint16_t)(block[0] | block[1] << 8));
+            float sum = 0.0f;
+            for (int i = 0; i < 32; ++i) sum += (float)(int8_t)block[2 + i] * x[b * 32 + i];
+            acc += d * sum;
+        }
+        y[r] = acc;
+    }
+}
+
+/* `split_blocks` (weights/src/q8_0.rs:17-31): the signed bytes in order, and the scales. */
+void oracle_q8_0_split(const uint8_t *blocks, long n_blocks, uint8_t *codes, uint8_t *scales) {
+    for (long b = 0; b < n_blocks; ++b) {
+        memcpy(scales + 2 * b, blocks + 34 * b, 2);
+        memcpy(codes + 32 * b, blocks + 34 * b + 2, 32);
+    }
+}

@@ -55,6 +55,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_bf16_matvec.argtypes = [_u16p, ctypes.c_long, ctypes.c_long, _f32p, _f32p]
         L.oracle_max_threads.restype = ctypes.c_int
         L.oracle_xorshift_values.argtypes = [ctypes.c_uint64, ctypes.c_long, _f32p]
+        _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+        L.oracle_q8_0_mul_vec.argtypes = [_u8p, ctypes.c_long, ctypes.c_long, _f32p, _f32p]
+        L.oracle_q8_0_split.argtypes = [_u8p, ctypes.c_long, _u8p, _u8p]
         _lib = L
     return _lib
 
@@ -89,6 +92,11 @@ def xorshift_values(seed: int, n: int) -> np.ndarray:
     out = np.zeros(n, np.float32)
     lib().oracle_xorshift_values(seed, n, out)
     return out
+
+
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    """IEEE binary16 bit patterns (round to nearest even) of an f32 array: scales of Q8_0 blocks."""
+    return np.ascontiguousarray(x, np.float32).astype(np.float16).view(np.uint16)
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

@@ -1,0 +1,114 @@
+"""Q8_0 products through the C ABI, the way the reference tests its own
+(metal-compute/tests/q8_0_and_gpt_oss_glue.rs:52-160): a repacked matrix with exact binary16
+scales of either sign, xorshift inputs in [-1, 1), gpt-oss's projection shapes and odd ones,
+against the float64 definition with the reference's bound (relative error < 1e-5), and against
+the CPU oracle's block-wise float32 product."""
+import numpy as np
+import pytest
+
+from loadngo_b200 import compute
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+SCALES = [(0x3800, 0.5), (0x2000, 0.0078125), (0xB600, -0.375), (0x3C00, 1.0), (0x1400, 0.0009765625), (0x4100, 2.5)]
+
+
+def q8_matrix(rows, cols, seed):
+    """`q8_matrix` of the reference's test: codes, scale bytes, every element's value."""
+    v = oracle.xorshift_values(seed, rows * cols)
+    codes = (v * np.float32(127.9)).astype(np.int8)        # `as i8` truncates toward zero, like astype
+    sv = oracle.xorshift_values(seed + 1, rows * cols // 32)
+    pick = (((sv + np.float32(1.0)) * np.float32(3.0)).astype(np.int64) + np.arange(sv.size)) % 6
+    bits = np.array([s[0] for s in SCALES], np.uint16)[pick]
+    vals = np.array([s[1] for s in SCALES], np.float64)[pick]
+    w = codes.astype(np.float64) * np.repeat(vals, 32)
+    return codes.view(np.uint8), bits.view(np.uint8), w.reshape(rows, cols)
+
+
+def run(gpu, kind, rows, cols, n):
+    codes, scales, w = q8_matrix(rows, cols, 7 + rows)
+    x = oracle.xorshift_values(11, n * cols)
+    bufs = [gpu.upload(codes), gpu.upload(scales), gpu.upload(x), gpu.buffer(n * rows * 4)]
+    batch = gpu.batch(bufs)
+    S = compute.Slice
+    matrix = (S(0, 0, codes.size), S(1, 0, scales.size))
+    xs, ys = S(2, 0, x.size * 4), S(3, 0, n * rows * 4)
+    if kind == "gemv":
+        batch.gemv_q8_0(matrix, xs, ys, rows, cols)
+    elif kind == "gemm":
+        batch.gemm_q8_0(matrix, xs, ys, rows, cols, n, (cols, rows))
+    else:
+        batch.gemm_q8_0_tiled(matrix, xs, ys, rows, cols, n, (cols, rows))
+    done = batch.run()
+    assert not isinstance(done.gpu_time, Exception), done.gpu_time
+    got = bufs[3].view(np.float32)[: n * rows].reshape(n, rows).copy()
+    for b in bufs:
+        b.free()
+    return got, w, x.reshape(n, cols), codes, scales
+
+
+@pytest.mark.parametrize("rows,cols,n,kind", [
+    (4096, 2880, 1, "gemv"), (512, 2880, 1, "gemv"), (37, 96, 1, "gemv"), (512, 2880, 5, "gemm"),
+    (37, 96, 13, "gemm"), (2880, 4096, 32, "tiled"), (512, 2880, 96, "tiled")])
+def test_q8_0_products_match_the_float64_definition(gpu, rows, cols, n, kind):
+    got, w, x, codes, scales = run(gpu, kind, rows, cols, n)
+    want = x.astype(np.float64) @ w.T
+    error = np.abs(got - want).max() / np.abs(want).max()
+    assert error < 1e-5, f"{rows} x {cols}, {n} positions, {kind}: relative error {error:e}"
+    # and the CPU oracle's block-wise float32 product on the first position
+    blocks = np.zeros((rows * cols // 32, 34), np.uint8)
+    blocks[:, :2] = scales.reshape(-1, 2)
+    blocks[:, 2:] = codes.reshape(-1, 32)
+    y = np.zeros(rows, np.float32)
+    oracle.lib().oracle_q8_0_mul_vec(np.ascontiguousarray(blocks.reshape(-1)), rows, cols, np.ascontiguousarray(x[0]), y)
+    assert np.abs(got[0] - y).max() <= 2e-5 * np.abs(want).max()
+
+
+def test_strided_positions_and_untouched_gaps(gpu):
+    """x rows and y rows further apart than their widths: only the named columns are read and
+    written (the reference's gemm_args contract, apple.rs:987-1013)."""
+    rows, cols, n, xs_, ys_ = 40, 64, 9, 80, 48
+    codes, scales, w = q8_matrix(rows, cols, 3)
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((n, xs_)).astype(np.float32)
+    x[:, cols:] = np.nan                                   # poison what must not be read
+    x_flat = x.reshape(-1)[: (n - 1) * xs_ + cols]
+    y0 = np.full((n - 1) * ys_ + rows, 7.0, np.float32)
+    bufs = [gpu.upload(codes), gpu.upload(scales), gpu.upload(x_flat), gpu.upload(y0)]
+    batch = gpu.batch(bufs)
+    S = compute.Slice
+    batch.gemm_q8_0((S(0, 0, codes.size), S(1, 0, scales.size)), S(2, 0, x_flat.size * 4), S(3, 0, y0.size * 4), rows,
+                    cols, n, (xs_, ys_))
+    assert not isinstance(batch.run().gpu_time, Exception)
+    got = bufs[3].view(np.float32)[: y0.size].copy()
+    want = x[:, :cols].astype(np.float64) @ w.T
+    for p in range(n):
+        assert np.abs(got[p * ys_: p * ys_ + rows] - want[p]).max() < 1e-5 * np.abs(want).max()
+        if p < n - 1:
+            assert np.all(got[p * ys_ + rows:(p + 1) * ys_] == 7.0)
+    for b in bufs:
+        b.free()
+
+
+def test_q8_0_rejects_what_the_reference_rejects(gpu):
+    """Partial blocks, strides, the tiled form's padding rule, misaligned operands
+    (apple.rs:1796-1806, 987-1013, 1862-1868; q8_0_and_gpt_oss_glue.rs:162-188)."""
+    bufs = [gpu.buffer(1 << 16) for _ in range(4)]
+    S = compute.Slice
+    m = (S(0, 0, 64 * 48), S(1, 0, 64 * 48 // 32 * 2))
+    batch = gpu.batch(bufs)
+    with pytest.raises(compute.DispatchError):
+        batch.gemv_q8_0(m, S(2, 0, 48 * 4), S(3, 0, 64 * 4), 64, 48)            # 48 is not whole blocks
+    m = (S(0, 0, 64 * 64), S(1, 0, 64 * 64 // 32 * 2))
+    with pytest.raises(compute.DispatchError):
+        batch.gemm_q8_0(m, S(2, 0, 4 * 64 * 4), S(3, 0, 4 * 64 * 4), 64, 64, 4, (62, 64))   # x stride below cols
+    with pytest.raises(compute.DispatchError):
+        batch.gemm_q8_0_tiled(m, S(2, 0, 4 * 64 * 4), S(3, 0, 4 * 64 * 4), 64, 64, 4, (64, 64))   # n % 32
+    with pytest.raises(compute.DispatchError):
+        batch.gemv_q8_0((S(0, 8, 64 * 64), m[1]), S(2, 0, 64 * 4), S(3, 0, 64 * 4), 64, 64)  # codes off a 16-byte boundary
+    with pytest.raises(compute.DispatchError):
+        batch.gemv_q8_0(m, S(2, 0, 64 * 4), S(2, 128, 64 * 4), 64, 64)          # y overlaps x
+    batch.gemv_q8_0(m, S(2, 0, 64 * 4), S(3, 0, 64 * 4), 64, 64)               # the batch is still usable
+    batch.drop()
+    for b in bufs:
+        b.free()

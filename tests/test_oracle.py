@@ -140,3 +140,30 @@ def test_bf16_cache_mode_only_rounds_what_is_appended():
     b.feed(q, k, v)
     assert np.array_equal(b.keys, oracle.round_bf16(f.keys))
     assert np.array_equal(b.values, f.values)   # v was bf16 already
+
+
+def test_q8_0_product_and_split_follow_the_block_definition():
+    """A Q8_0 block is a binary16 scale d and 32 signed bytes q, element i = d * q[i]
+    (weights/src/q8_0.rs:1-6): the oracle's product against that definition in float64, its
+    split against plain slicing, and the scale decoder on known binary16 values (normal, subnormal,
+    negative: the scales of metal-compute/tests/q8_0_and_gpt_oss_glue.rs:58-65 among them)."""
+    rng = np.random.default_rng(5)
+    rows, cols = 7, 96
+    scale_bits = np.array([0x3800, 0x2000, 0xB600, 0x3C00, 0x1400, 0x4100, 0x0001, 0x03ff, 0x8400], np.uint16)
+    scale_vals = np.array([0.5, 0.0078125, -0.375, 1.0, 0.0009765625, 2.5, 2.0 ** -24, 1023 * 2.0 ** -24, -2.0 ** -14])
+    pick = rng.integers(0, len(scale_bits), rows * cols // 32)
+    q = rng.integers(-128, 128, (rows * cols // 32, 32)).astype(np.int8)
+    blocks = np.zeros((rows * cols // 32, 34), np.uint8)
+    blocks[:, :2] = scale_bits[pick].view(np.uint8).reshape(-1, 2)
+    blocks[:, 2:] = q.view(np.uint8)
+    x = rng.standard_normal(cols).astype(np.float32)
+    y = np.zeros(rows, np.float32)
+    oracle.lib().oracle_q8_0_mul_vec(np.ascontiguousarray(blocks.reshape(-1)), rows, cols, x, y)
+    w = (q.astype(np.float64) * scale_vals[pick][:, None]).reshape(rows, cols)
+    want = w @ x.astype(np.float64)
+    assert np.abs(y - want).max() <= 1e-5 * np.abs(want).max()
+    codes = np.zeros(rows * cols, np.uint8)
+    scales = np.zeros(rows * cols // 32 * 2, np.uint8)
+    oracle.lib().oracle_q8_0_split(np.ascontiguousarray(blocks.reshape(-1)), rows * cols // 32, codes, scales)
+    assert np.array_equal(codes, blocks[:, 2:].reshape(-1))
+    assert np.array_equal(scales, blocks[:, :2].reshape(-1))
