@@ -40,6 +40,10 @@ def load(reference_root: str):
     reader = gguf.GGUFReader(os.path.join(d, "model.gguf"))
     meta = {k: f.contents() for k, f in reader.fields.items() if k.startswith("gpt-oss.")}
     tensors = {t.name: np.array(dequantize(t.data, t.tensor_type), np.float32) for t in reader.tensors}
+    # the attention projections also as they are stored: ggml Q8_0 blocks, row after row
+    for t in reader.tensors:
+        if t.tensor_type == gguf.GGMLQuantizationType.Q8_0 and ".attn_" in t.name:
+            tensors[t.name + ":q8_0"] = np.ascontiguousarray(t.data, np.uint8).reshape(-1)
     with open(os.path.join(d, "oracle.json")) as fh:
         ids = json.load(fh)["ids"]
     logits = np.fromfile(os.path.join(d, "logits.f32"), np.float32)
@@ -105,6 +109,8 @@ def replay(meta, T, ids, mutation: str | None = None, record: dict | None = None
     for pos, token in enumerate(ids):
         h = T["token_embd.weight"][token].copy()
         for l in range(layers):
+            if record is not None:
+                record.setdefault(f"l{l}_h_in", []).append(h.copy())
             x = rms_norm(h, T[f"blk.{l}.attn_norm.weight"], eps)
             q = T[f"blk.{l}.attn_q.weight"] @ x + T[f"blk.{l}.attn_q.bias"]
             k = T[f"blk.{l}.attn_k.weight"] @ x + T[f"blk.{l}.attn_k.bias"]
@@ -119,6 +125,9 @@ def replay(meta, T, ids, mutation: str | None = None, record: dict | None = None
             o = T[f"blk.{l}.attn_output.weight"] @ att.reshape(-1) + T[f"blk.{l}.attn_output.bias"]
             h = h + o.astype(np.float32)
             x = rms_norm(h, T[f"blk.{l}.post_attention_norm.weight"], eps)
+            if record is not None:
+                record.setdefault(f"l{l}_h_att", []).append(h.copy())
+                record.setdefault(f"l{l}_x_ffn", []).append(x.copy())
             h = h + experts(T, l, x, used)
         x = rms_norm(h, T["output_norm.weight"], eps)
         all_logits.append((T["output.weight"] @ x).astype(np.float32))
@@ -158,8 +167,28 @@ def main():
         "positions": len(ids), "worst_logit_error": worst,
         "mutations": dict(zip(mutations, errs)),
     }))
+    # the block-level vectors (residual stream in and out of the attention half of each layer, the
+    # Q8_0 projections as stored) go to a file of their own
+    block = {k: out.pop(k) for k in [k for k in out if k.endswith(("_h_in", "_h_att", "_x_ffn"))]}
+    for l in range(meta["gpt-oss.block_count"]):
+        for name in ("attn_q", "attn_k", "attn_v", "attn_output"):
+            block[f"l{l}_{name}_q8_0"] = T[f"blk.{l}.{name}.weight:q8_0"]
+            block[f"l{l}_{name}_bias"] = T[f"blk.{l}.{name}.bias"].astype(np.float32)
+        block[f"l{l}_attn_norm"] = T[f"blk.{l}.attn_norm.weight"].astype(np.float32)
+        block[f"l{l}_ffn_norm"] = T[f"blk.{l}.post_attention_norm.weight"].astype(np.float32)
+        block[f"l{l}_sinks"] = out[f"l{l}_sinks"]
+    block["meta"] = np.array(json.dumps({
+        "layers": meta["gpt-oss.block_count"], "hidden": int(T["token_embd.weight"].shape[1]),
+        "heads": meta["gpt-oss.attention.head_count"], "kv_heads": meta["gpt-oss.attention.head_count_kv"],
+        "dim": meta["gpt-oss.attention.key_length"], "window": meta["gpt-oss.attention.sliding_window"],
+        "eps": float(meta["gpt-oss.attention.layer_norm_rms_epsilon"]),
+        "theta": meta["gpt-oss.rope.freq_base"], "factor": meta["gpt-oss.rope.scaling.factor"],
+        "original_context": meta["gpt-oss.rope.scaling.original_context_length"], "positions": len(ids)}))
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tiny_attention.npz")
     np.savez_compressed(path, **out)
+    print(f"wrote {path} ({os.path.getsize(path)} bytes)")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tiny_block.npz")
+    np.savez_compressed(path, **block)
     print(f"wrote {path} ({os.path.getsize(path)} bytes)")
 
 

@@ -297,3 +297,115 @@ def test_tiny_fixture_through_the_reference_call_sequence(gpu, chunks):
         assert worst < 1e-4, f"layer {l}: worst attention error {worst}"
         for b in buffers:
             b.free()
+
+
+BLOCK_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_block.npz")
+
+
+def _split_q8_0(blocks: np.ndarray):
+    """`split_blocks` (weights/src/q8_0.rs:17-31) through the oracle."""
+    n = blocks.size // 34
+    codes, scales = np.zeros(n * 32, np.uint8), np.zeros(n * 2, np.uint8)
+    oracle.lib().oracle_q8_0_split(np.ascontiguousarray(blocks), n, codes, scales)
+    return codes, scales
+
+
+@pytest.mark.parametrize("chunks", [[1] * 40, [8] * 5, [33, 7]])
+def test_tiny_fixture_whole_encode_attention_with_the_stored_q8_0_weights(gpu, chunks):
+    """Everything `GpuModel::encode_attention` records (gpt-oss/src/gpu.rs:703-827), call for call,
+    on the tiny fixture's own weights as the GGUF stores them (Q8_0 projections with biases):
+    copy H to X, RMSNorm, the three projections (gemv for one position, the plain product below
+    32, the tiled one on n rounded up to 32 from there), biases, rotary, the ring append,
+    grouped attention with sinks, output projection, bias, residual add, and the copy + norm that
+    leaves the experts' input in X.  The residual stream going in is the golden one of each
+    layer (the experts between the layers are not part of this path); H and X coming out are
+    compared with the golden vectors made by the pinned oracle replay."""
+    g = np.load(BLOCK_GOLDEN)
+    meta = json.loads(str(g["meta"]))
+    hidden, heads, kv_heads, dim, positions = (meta[k] for k in ("hidden", "heads", "kv_heads", "dim", "positions"))
+    qw, kw, eps = heads * dim, kv_heads * dim, meta["eps"]
+    rope = dict(head_dim=dim, theta=meta["theta"], factor=meta["factor"], original_context=float(meta["original_context"]))
+    chunk = max(chunks)
+    pad = -(-chunk // 32) * 32
+    f = lambda b, row, w, rows: Slice(b, row * w * 4, rows * w * 4)
+    for l in range(meta["layers"]):
+        sliding = l % 2 == 0
+        window = meta["window"] if sliding else FULL
+        slots = -(-(meta["window"] + chunk) // 32) * 32 if sliding else -(-positions // 32) * 32
+        H, X, Q, K, V, ATT, TMP, TABLE, KC, VC = range(10)
+        buffers = [gpu.buffer(pad * w * 4) for w in (hidden, hidden, qw, kw, kw, qw, hidden, dim)]
+        buffers += [gpu.buffer(slots * kw * 4), gpu.buffer(slots * kw * 4)]
+        for b in buffers:
+            b.zero()
+        # the layer's weights as residents, as `GpuModel::load` keeps them
+        res = {}
+        for name in ("attn_q", "attn_k", "attn_v", "attn_output"):
+            codes, scales = _split_q8_0(g[f"l{l}_{name}_q8_0"])
+            res[name] = (gpu.resident(codes), gpu.resident(scales), gpu.resident(g[f"l{l}_{name}_bias"]))
+        res["attn_norm"], res["ffn_norm"] = gpu.resident(g[f"l{l}_attn_norm"]), gpu.resident(g[f"l{l}_ffn_norm"])
+        res["sinks"] = gpu.resident(g[f"l{l}_sinks"])
+
+        def mul(batch, name, rows, cols, x, y, n):           # Q8::mul, gpu.rs:121-137
+            tiled = n >= 32
+            n_run = -(-n // 32) * 32 if tiled else n
+            x, y = Slice(x.buffer, x.offset, n_run * cols * 4), Slice(y.buffer, y.offset, n_run * rows * 4)
+            m = (batch.attach(res[name][0]), batch.attach(res[name][1]))
+            if n == 1:
+                batch.gemv_q8_0(m, x, y, rows, cols)
+            elif tiled:
+                batch.gemm_q8_0_tiled(m, x, y, rows, cols, n_run, (cols, rows))
+            else:
+                batch.gemm_q8_0(m, x, y, rows, cols, n, (cols, rows))
+
+        start, worst_h, worst_x = 0, 0.0, 0.0
+        for n in chunks:
+            buffers[H].write(g[f"l{l}_h_in"][start:start + n])
+            buffers[TABLE].write(compute.rope_table(start, n, **rope))
+            batch = gpu.batch(buffers)
+            rows_of = lambda b, w: f(b, 0, w, n)
+            batch.copy_rows((rows_of(H, hidden), hidden), (rows_of(X, hidden), hidden), n, hidden)
+            batch.rmsnorm_rows((rows_of(X, hidden), batch.attach(res["attn_norm"])), n, (hidden, hidden), eps)
+            mul(batch, "attn_q", qw, hidden, rows_of(X, hidden), rows_of(Q, qw), n)
+            mul(batch, "attn_k", kw, hidden, rows_of(X, hidden), rows_of(K, kw), n)
+            mul(batch, "attn_v", kw, hidden, rows_of(X, hidden), rows_of(V, kw), n)
+            for buf, name, width in ((Q, "attn_q", qw), (K, "attn_k", kw), (V, "attn_v", kw)):
+                batch.add_rows(rows_of(buf, width), (batch.attach(res[name][2]), 0), n, width)
+            table = rows_of(TABLE, dim)
+            batch.rotate_halves(rows_of(Q, qw), table, n, (heads, dim))
+            batch.rotate_halves(rows_of(K, kw), table, n, (kv_heads, dim))
+            done_rows = 0
+            while done_rows < n:
+                row = (start + done_rows) % slots
+                run = min(n - done_rows, slots - row)
+                for src, dst in ((K, KC), (V, VC)):
+                    batch.copy_rows((f(src, done_rows, kw, run), kw), (f(dst, row, kw, run), kw), run, kw)
+                done_rows += run
+            s = GroupedShape(n, start, heads, kv_heads, dim, window, slots, 1.0 / float(np.sqrt(np.float32(dim))))
+            sinks = batch.attach(res["sinks"])
+            if n >= 32:
+                padded, end = -(-n // 32) * 32, start + n
+                rows = slots if slots < end else -(-end // 32) * 32
+                batch.attention_grouped_tiled_with_sinks((f(Q, 0, qw, padded), f(KC, 0, kw, rows), f(VC, 0, kw, rows)),
+                                                         sinks, f(ATT, 0, qw, padded), s)
+            else:
+                rows = min(slots, start + n)
+                batch.attention_grouped_with_sinks((rows_of(Q, qw), f(KC, 0, kw, rows), f(VC, 0, kw, rows)), sinks,
+                                                   rows_of(ATT, qw), s)
+            mul(batch, "attn_output", hidden, qw, rows_of(ATT, qw), rows_of(TMP, hidden), n)
+            batch.add_rows(rows_of(TMP, hidden), (batch.attach(res["attn_output"][2]), 0), n, hidden)
+            batch.add_rows(rows_of(H, hidden), (rows_of(TMP, hidden), hidden), n, hidden)
+            batch.copy_rows((rows_of(H, hidden), hidden), (rows_of(X, hidden), hidden), n, hidden)
+            batch.rmsnorm_rows((rows_of(X, hidden), batch.attach(res["ffn_norm"])), n, (hidden, hidden), eps)
+            done = batch.run()
+            assert not isinstance(done.gpu_time, Exception), done.gpu_time
+            got_h = buffers[H].as_f32()[: n * hidden].reshape(n, hidden)
+            got_x = buffers[X].as_f32()[: n * hidden].reshape(n, hidden)
+            worst_h = max(worst_h, float(np.abs(got_h - g[f"l{l}_h_att"][start:start + n]).max()))
+            worst_x = max(worst_x, float(np.abs(got_x - g[f"l{l}_x_ffn"][start:start + n]).max()))
+            start += n
+        assert worst_h < 2e-4 and worst_x < 2e-4, f"layer {l}: residual {worst_h}, experts' input {worst_x}"
+        for b in buffers:
+            b.free()
+        for v in res.values():
+            for r in (v if isinstance(v, tuple) else (v,)):
+                r.free()

@@ -167,3 +167,27 @@ def test_q8_0_product_and_split_follow_the_block_definition():
     oracle.lib().oracle_q8_0_split(np.ascontiguousarray(blocks.reshape(-1)), rows * cols // 32, codes, scales)
     assert np.array_equal(codes, blocks[:, 2:].reshape(-1))
     assert np.array_equal(scales, blocks[:, :2].reshape(-1))
+
+
+def test_q8_0_product_reproduces_the_tiny_fixtures_projections():
+    """The oracle's Q8_0 product on the fixture's stored blocks gives the q, k, v that the pinned
+    replay computed from the `gguf` package's own dequantisation of the same tensors
+    (tests/golden/make_tiny_golden.py): two independent decoders of the format agree."""
+    import json
+    import os
+    here = os.path.dirname(__file__)
+    blk = np.load(os.path.join(here, "golden", "tiny_block.npz"))
+    att = np.load(os.path.join(here, "golden", "tiny_attention.npz"))
+    meta = json.loads(str(blk["meta"]))
+    hidden = meta["hidden"]
+    for l in range(meta["layers"]):
+        for p in (0, 17, meta["positions"] - 1):
+            x = np.zeros(hidden, np.float32)
+            oracle.lib().oracle_rms_norm(np.ascontiguousarray(blk[f"l{l}_h_in"][p]), blk[f"l{l}_attn_norm"],
+                                         meta["eps"], hidden, x)
+            for name, key in (("attn_q", "q"), ("attn_k", "k"), ("attn_v", "v")):
+                want = att[f"l{l}_{key}"][p].reshape(-1)
+                y = np.zeros(want.size, np.float32)
+                oracle.lib().oracle_q8_0_mul_vec(np.ascontiguousarray(blk[f"l{l}_{name}_q8_0"]), want.size, hidden, x, y)
+                y += blk[f"l{l}_{name}_bias"]
+                assert np.abs(y - want).max() < 2e-5, (l, p, name)
