@@ -330,6 +330,29 @@ int cc_batch_gemm_q8_0(cc_batch *batch, cc_slice codes, cc_slice scales, cc_slic
                        uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride);
 int cc_batch_gemm_q8_0_tiled(cc_batch *batch, cc_slice codes, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
                              uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride);
+/* The routed experts of one decode position, as GpuModel::encode_routed_experts records them
+ * (gpt-oss/src/gpu.rs:829-888); all float32.
+ * gemv_f32 (apple.rs:2000-2039): y = W x (+ bias), W rows x cols row-major, cols % 4 == 0, w and x
+ *   on 16-byte boundaries; bias NULL for none.
+ * topk_softmax (apple.rs:2042-2074): per row of `experts` logits the k largest (ties: lower index
+ *   first) as u32 into ids [n][k], their softmax over just those into weights [n][k]; k <= 16.
+ * gemv_mxfp4_selected (apple.rs:2082-2121): y[j] = W[ids[j]] x[j], j < k; `matrices` rows x cols
+ *   MXFP4 matrices one after another (elements two per byte, even element in the low nibble; one
+ *   E8M0 scale byte per 32: weights/src/mxfp4.rs); x[j] at j * x_stride floats (0: one x for all).
+ * clamped_swiglu_selected (apple.rs:2126-2160): out = (clamp(up + ub, -limit, limit) + 1) * g *
+ *   sigmoid(alpha g), g = min(gate + gb, limit), biases rows ids[j] of [experts][width].
+ * moe_combine (apple.rs:2164-2191): h += sum_j weights[j] * (y[j] + bias[ids[j]]). */
+int cc_batch_gemv_f32(cc_batch *batch, cc_slice w, const cc_slice *bias, cc_slice x, cc_slice y, uint64_t rows,
+                      uint64_t cols);
+int cc_batch_topk_softmax(cc_batch *batch, cc_slice logits, cc_slice ids, cc_slice weights, uint64_t n, uint64_t experts,
+                          uint64_t k);
+int cc_batch_gemv_mxfp4_selected(cc_batch *batch, cc_slice elements, cc_slice scales, uint64_t matrices, cc_slice ids,
+                                 cc_slice x, uint64_t x_stride, cc_slice y, uint64_t rows, uint64_t cols, uint64_t k);
+int cc_batch_clamped_swiglu_selected(cc_batch *batch, cc_slice gate, cc_slice up, cc_slice gate_bias, cc_slice up_bias,
+                                     uint64_t experts, cc_slice ids, cc_slice out, uint64_t k, uint64_t width, float limit,
+                                     float alpha);
+int cc_batch_moe_combine(cc_batch *batch, cc_slice h, cc_slice y, cc_slice bias, uint64_t experts, cc_slice ids,
+                         cc_slice weights, uint64_t k, uint64_t width);
 /* Batch::add_rows (apple.rs:1886-1911): dst[r] += src[r * src_stride ..]; stride 0 = a bias. */
 int cc_batch_add_rows(cc_batch *batch, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
                       uint64_t width);

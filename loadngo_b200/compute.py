@@ -173,6 +173,13 @@ SYMBOLS = {
     "cc_batch_copy_rows": (c_int, [c_void_p, Slice, c_uint64, Slice, c_uint64, c_uint64, c_uint64]),
     "cc_batch_rmsnorm_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64, c_float]),
     "cc_batch_add_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_gemv_f32": (c_int, [c_void_p, Slice, POINTER(Slice), Slice, Slice, c_uint64, c_uint64]),
+    "cc_batch_topk_softmax": (c_int, [c_void_p, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_gemv_mxfp4_selected": (c_int, [c_void_p, Slice, Slice, c_uint64, Slice, Slice, c_uint64, Slice, c_uint64,
+                                             c_uint64, c_uint64]),
+    "cc_batch_clamped_swiglu_selected": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, Slice, Slice, c_uint64,
+                                                 c_uint64, c_float, c_float]),
+    "cc_batch_moe_combine": (c_int, [c_void_p, Slice, Slice, Slice, c_uint64, Slice, Slice, c_uint64, c_uint64]),
     "cc_batch_gemv_q8_0": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64]),
     "cc_batch_gemm_q8_0": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64, c_uint64,
                                    c_uint64]),
@@ -409,6 +416,27 @@ class Batch:
     def add_rows(self, dst: Slice, src, rows: int, width: int) -> None:
         s, ss = src
         check(lib().cc_batch_add_rows(self._h, dst, s, ss, rows, width))
+
+    def gemv_f32(self, w_bias, x: Slice, y: Slice, rows: int, cols: int) -> None:
+        """`Batch::gemv_f32` (apple.rs:2000-2039); `w_bias` = (w, bias or None)."""
+        w, bias = w_bias
+        check(lib().cc_batch_gemv_f32(self._h, w, _opt(bias), x, y, rows, cols))
+
+    def topk_softmax(self, logits: Slice, ids_weights, n: int, experts_k) -> None:
+        (ids, weights), (experts, k) = ids_weights, experts_k
+        check(lib().cc_batch_topk_softmax(self._h, logits, ids, weights, n, experts, k))
+
+    def gemv_mxfp4_selected(self, matrices, ids: Slice, x_stride, y: Slice, rows_cols, k: int) -> None:
+        (elements, scales, count), (x, stride), (rows, cols) = matrices, x_stride, rows_cols
+        check(lib().cc_batch_gemv_mxfp4_selected(self._h, elements, scales, count, ids, x, stride, y, rows, cols, k))
+
+    def clamped_swiglu_selected(self, gate_up, biases, ids: Slice, out: Slice, k_width, limit_alpha) -> None:
+        (gate, up), (gb, ub, experts), (k, width), (limit, alpha) = gate_up, biases, k_width, limit_alpha
+        check(lib().cc_batch_clamped_swiglu_selected(self._h, gate, up, gb, ub, experts, ids, out, k, width, limit, alpha))
+
+    def moe_combine(self, h: Slice, y_bias, ids_weights, k_width) -> None:
+        (y, bias, experts), (ids, weights), (k, width) = y_bias, ids_weights, k_width
+        check(lib().cc_batch_moe_combine(self._h, h, y, bias, experts, ids, weights, k, width))
 
     def gemv_q8_0(self, matrix, x: Slice, y: Slice, rows: int, cols: int) -> None:
         """`Batch::gemv_q8_0` (apple.rs:1812-1830); `matrix` = (codes, scales)."""

@@ -875,6 +875,137 @@ extern "C" int cc_batch_gemm_q8_0_tiled(cc_batch *b, cc_slice codes, cc_slice sc
     return record_q8_0(b, "gemm_q8_0_tiled", codes, scales, x, y, rows, cols, n, x_stride, y_stride);
 }
 
+// ---- the routed experts of a decode position (apple.rs:2000-2191) ---------------------------
+
+extern "C" int cc_batch_gemv_f32(cc_batch *b, cc_slice w, const cc_slice *bias, cc_slice x, cc_slice y, uint64_t rows,
+                                 uint64_t cols) {
+    if (!b) return fail(CC_DISPATCH, "gemv_f32: null batch");
+    if (rows == 0 || cols == 0 || cols % 4 != 0)
+        return fail(CC_DISPATCH, "unsupported f32 product %llu x %llu", (unsigned long long)rows, (unsigned long long)cols);
+    uint32_t r, c, tmp;
+    if (narrow(rows, &r) || narrow(cols, &c) || narrow(rows * cols, &tmp)) return CC_DISPATCH;
+    uint8_t *pw, *px, *py, *pb = nullptr;
+    if (int rc = check(b, "weights", w, rows * cols * 4, 16, &pw)) return rc;
+    if (int rc = check(b, "x", x, cols * 4, 16, &px)) return rc;
+    if (int rc = check(b, "y", y, rows * 4, 4, &py)) return rc;
+    if (bias)
+        if (int rc = check(b, "bias", *bias, rows * 4, 4, &pb)) return rc;
+    if (int rc = check_output(b, y, {&w, &x, bias})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_gemv_f32(reinterpret_cast<const float *>(pw), reinterpret_cast<const float *>(px),
+                            reinterpret_cast<const float *>(pb), reinterpret_cast<float *>(py), r, c, s);
+        return CC_OK;
+    });
+    wrote(b, y);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_topk_softmax(cc_batch *b, cc_slice logits, cc_slice ids, cc_slice weights, uint64_t n,
+                                     uint64_t experts, uint64_t k) {
+    if (!b) return fail(CC_DISPATCH, "topk_softmax: null batch");
+    if (n == 0 || k == 0 || k > 16 || k > experts)
+        return fail(CC_DISPATCH, "unsupported top-%llu of %llu over %llu rows", (unsigned long long)k,
+                    (unsigned long long)experts, (unsigned long long)n);
+    uint32_t nn, e, kk, tmp;
+    if (narrow(n, &nn) || narrow(experts, &e) || narrow(k, &kk) || narrow(n * experts, &tmp)) return CC_DISPATCH;
+    uint8_t *pl, *pi, *pw;
+    if (int rc = check(b, "logits", logits, n * experts * 4, 4, &pl)) return rc;
+    if (int rc = check(b, "ids", ids, n * k * 4, 4, &pi)) return rc;
+    if (int rc = check(b, "weights", weights, n * k * 4, 4, &pw)) return rc;
+    if (int rc = check_output(b, ids, {&logits})) return rc;
+    if (int rc = check_output(b, weights, {&logits, &ids})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_topk_softmax(reinterpret_cast<const float *>(pl), reinterpret_cast<uint32_t *>(pi),
+                                reinterpret_cast<float *>(pw), nn, e, kk, s);
+        return CC_OK;
+    });
+    wrote(b, ids);
+    wrote(b, weights);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_gemv_mxfp4_selected(cc_batch *b, cc_slice elements, cc_slice scales, uint64_t matrices, cc_slice ids,
+                                            cc_slice x, uint64_t x_stride, cc_slice y, uint64_t rows, uint64_t cols,
+                                            uint64_t k) {
+    if (!b) return fail(CC_DISPATCH, "gemv_mxfp4_selected: null batch");
+    if (rows == 0 || cols == 0 || cols % 32 != 0 || k == 0 || matrices == 0 || (x_stride != 0 && x_stride < cols))
+        return fail(CC_DISPATCH, "unsupported selected MXFP4 product: %llu of %llu %llu x %llu, x stride %llu",
+                    (unsigned long long)k, (unsigned long long)matrices, (unsigned long long)rows, (unsigned long long)cols,
+                    (unsigned long long)x_stride);
+    uint32_t r, c, kk, xs, m, tmp;
+    if (narrow(rows, &r) || narrow(cols, &c) || narrow(k, &kk) || narrow(x_stride, &xs) || narrow(matrices, &m) ||
+        narrow(rows * cols, &tmp))
+        return CC_DISPATCH;
+    uint8_t *pe, *ps, *pi, *px, *py;
+    if (int rc = check(b, "elements", elements, matrices * rows * cols / 2, 16, &pe)) return rc;
+    if (int rc = check(b, "scales", scales, matrices * rows * cols / 32, 1, &ps)) return rc;
+    if (int rc = check(b, "ids", ids, k * 4, 4, &pi)) return rc;
+    if (int rc = check(b, "x", x, ((k - 1) * x_stride + cols) * 4, 16, &px)) return rc;
+    if (int rc = check(b, "y", y, k * rows * 4, 4, &py)) return rc;
+    if (int rc = check_output(b, y, {&elements, &scales, &ids, &x})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_gemv_mxfp4_selected(pe, ps, reinterpret_cast<const uint32_t *>(pi), reinterpret_cast<const float *>(px),
+                                       reinterpret_cast<float *>(py), r, c, kk, xs, m, s);
+        return CC_OK;
+    });
+    wrote(b, y);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_clamped_swiglu_selected(cc_batch *b, cc_slice gate, cc_slice up, cc_slice gate_bias, cc_slice up_bias,
+                                                uint64_t experts, cc_slice ids, cc_slice out, uint64_t k, uint64_t width,
+                                                float limit, float alpha) {
+    if (!b) return fail(CC_DISPATCH, "clamped_swiglu_selected: null batch");
+    if (k == 0 || width == 0 || experts == 0) return fail(CC_DISPATCH, "empty clamped_swiglu_selected");
+    uint32_t kk, w, e, tmp;
+    if (narrow(k, &kk) || narrow(width, &w) || narrow(experts, &e) || narrow(k * width, &tmp)) return CC_DISPATCH;
+    uint8_t *pg, *pu, *pgb, *pub, *pi, *po;
+    if (int rc = check(b, "gate", gate, k * width * 4, 4, &pg)) return rc;
+    if (int rc = check(b, "up", up, k * width * 4, 4, &pu)) return rc;
+    if (int rc = check(b, "out", out, k * width * 4, 4, &po)) return rc;
+    if (int rc = check(b, "gate_bias", gate_bias, experts * width * 4, 4, &pgb)) return rc;
+    if (int rc = check(b, "up_bias", up_bias, experts * width * 4, 4, &pub)) return rc;
+    if (int rc = check(b, "ids", ids, k * 4, 4, &pi)) return rc;
+    if (int rc = check_output(b, out, {&gate, &up, &gate_bias, &up_bias, &ids})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_clamped_swiglu_selected(reinterpret_cast<const float *>(pg), reinterpret_cast<const float *>(pu),
+                                           reinterpret_cast<const float *>(pgb), reinterpret_cast<const float *>(pub),
+                                           reinterpret_cast<const uint32_t *>(pi), reinterpret_cast<float *>(po), kk, w, e,
+                                           limit, alpha, s);
+        return CC_OK;
+    });
+    wrote(b, out);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_moe_combine(cc_batch *b, cc_slice h, cc_slice y, cc_slice bias, uint64_t experts, cc_slice ids,
+                                    cc_slice weights, uint64_t k, uint64_t width) {
+    if (!b) return fail(CC_DISPATCH, "moe_combine: null batch");
+    if (k == 0 || width == 0 || experts == 0) return fail(CC_DISPATCH, "empty moe_combine");
+    uint32_t kk, w, e, tmp;
+    if (narrow(k, &kk) || narrow(width, &w) || narrow(experts, &e) || narrow(experts * width, &tmp)) return CC_DISPATCH;
+    uint8_t *ph, *py, *pb, *pi, *pw;
+    if (int rc = check(b, "h", h, width * 4, 4, &ph)) return rc;
+    if (int rc = check(b, "y", y, k * width * 4, 4, &py)) return rc;
+    if (int rc = check(b, "bias", bias, experts * width * 4, 4, &pb)) return rc;
+    if (int rc = check(b, "ids", ids, k * 4, 4, &pi)) return rc;
+    if (int rc = check(b, "weights", weights, k * 4, 4, &pw)) return rc;
+    if (int rc = check_output(b, h, {&y, &bias, &ids, &weights})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_moe_combine(reinterpret_cast<float *>(ph), reinterpret_cast<const float *>(py),
+                               reinterpret_cast<const float *>(pb), reinterpret_cast<const uint32_t *>(pi),
+                               reinterpret_cast<const float *>(pw), w, kk, e, s);
+        return CC_OK;
+    });
+    wrote(b, h);
+    ++b->dispatches;
+    return CC_OK;
+}
+
 extern "C" int cc_batch_add_rows(cc_batch *b, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
                                  uint64_t width) {
     if (!b) return fail(CC_DISPATCH, "add_rows: null batch");

@@ -29,4 +29,18 @@ void launch_attention_grouped(const float *q, const float *k, const float *v, fl
 void launch_q8_0(const int8_t *codes, const void *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
                  uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream);
 
+// The routed-experts kernels (moe.cu).
+void launch_gemv_f32(const float *w, const float *x, const float *bias, float *y, uint32_t rows, uint32_t cols,
+                     cudaStream_t stream);
+void launch_topk_softmax(const float *logits, uint32_t *ids, float *weights, uint32_t n, uint32_t experts, uint32_t k,
+                         cudaStream_t stream);
+void launch_gemv_mxfp4_selected(const uint8_t *elements, const uint8_t *scales, const uint32_t *ids, const float *x,
+                                float *y, uint32_t rows, uint32_t cols, uint32_t k, uint32_t x_stride, uint32_t matrices,
+                                cudaStream_t stream);
+void launch_clamped_swiglu_selected(const float *gate, const float *up, const float *gate_bias, const float *up_bias,
+                                    const uint32_t *ids, float *out, uint32_t rows, uint32_t width, uint32_t experts,
+                                    float limit, float alpha, cudaStream_t stream);
+void launch_moe_combine(float *h, const float *y, const float *bias, const uint32_t *ids, const float *weights,
+                        uint32_t width, uint32_t k, uint32_t experts, cudaStream_t stream);
+
 }  // namespace cc

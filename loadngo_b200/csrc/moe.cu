@@ -1,0 +1,186 @@
+// The routed-experts half of a gpt-oss layer for one decode position: router product, top-k with
+// softmax, the chosen experts' MXFP4 products, the clamped SwiGLU with per-expert biases, and the
+// weighted sum into the residual.
+//
+// Replaces `gemv_f32`, `topk_softmax`, `gemv_mxfp4_selected`, `clamped_swiglu_selected` and
+// `moe_combine` (metal-compute/src/kernels.metal:1729-1935; host entries
+// metal-compute/src/apple.rs:2000-2191), which `GpuModel::encode_routed_experts` records per layer
+// (gpt-oss/src/gpu.rs:829-888); the arithmetic is `Model::route` and `Model::experts`
+// (gpt-oss/src/model.rs:480-548).  Everything is float32, as in the reference.
+//
+// MXFP4 (OCP MX v1.0, weights/src/mxfp4.rs:1-45): blocks of 32 E2M1 elements, two per byte with the
+// even element in the low nibble, and one E8M0 scale byte per block (2^(s - 127); 0xFF is NaN,
+// 0 is 2^-127).  The products are HBM-bound (half a byte per element): a warp owns a row, a lane
+// reads a block's 16 bytes in one load and the 32 activations it meets through L1.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "legacy.cuh"
+
+namespace cc {
+namespace {
+
+constexpr int kMoeWarps = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// y = W x (+ b), float32 row-major W, one warp per row (kernels.metal:1729-1755).
+__global__ void __launch_bounds__(kMoeWarps * 32) gemv_f32_kernel(const float *__restrict__ w, const float *__restrict__ x,
+                                                                  const float *__restrict__ b, float *__restrict__ y,
+                                                                  uint32_t rows, uint32_t cols) {
+    const uint32_t row = blockIdx.x * kMoeWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float4 *w4 = reinterpret_cast<const float4 *>(w + static_cast<size_t>(row) * cols);
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    float acc = 0.f;
+    for (uint32_t i = lane; i < cols / 4; i += 32) {
+        const float4 a = w4[i], c = __ldg(x4 + i);
+        acc += a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[row] = acc + (b ? b[row] : 0.f);
+}
+
+// Per row of logits: the k largest (equal logits: the lower index first) and their softmax over
+// just those k (kernels.metal:1766-1810; Model::route, model.rs:482-497).  One thread per row.
+__global__ void topk_softmax_kernel(const float *__restrict__ logits, uint32_t *__restrict__ ids,
+                                    float *__restrict__ weights, uint32_t n, uint32_t experts, uint32_t k) {
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= n) return;
+    const float *row = logits + static_cast<size_t>(gid) * experts;
+    uint32_t picked[16];
+    float value[16];
+    for (uint32_t j = 0; j < k; ++j) {
+        uint32_t best = 0xffffffffu;
+        float best_value = -INFINITY;
+        for (uint32_t e = 0; e < experts; ++e) {
+            bool taken = false;
+            for (uint32_t i = 0; i < j; ++i) taken = taken || picked[i] == e;
+            if (!taken && (best == 0xffffffffu || row[e] > best_value)) {   // strictly greater: ties keep the lower index
+                best = e;
+                best_value = row[e];
+            }
+        }
+        picked[j] = best;
+        value[j] = best_value;
+    }
+    const float largest = value[0];
+    float total = 0.f;
+    for (uint32_t j = 0; j < k; ++j) {
+        value[j] = expf(value[j] - largest);
+        total += value[j];
+    }
+    for (uint32_t j = 0; j < k; ++j) {
+        ids[static_cast<size_t>(gid) * k + j] = picked[j];
+        weights[static_cast<size_t>(gid) * k + j] = value[j] / total;
+    }
+}
+
+__device__ __forceinline__ float e8m0(uint32_t s) {
+    if (s == 0xffu) return __int_as_float(0x7fc00000);
+    return s == 0 ? __int_as_float(0x00400000) : __int_as_float(static_cast<int>(s << 23));
+}
+
+// Eight packed elements (one 32-bit word, low nibble first) dotted with eight activations.
+__device__ __forceinline__ float dot_e2m1x8(uint32_t word, const float *lut, float4 x0, float4 x1) {
+    return lut[word & 15] * x0.x + lut[(word >> 4) & 15] * x0.y + lut[(word >> 8) & 15] * x0.z +
+           lut[(word >> 12) & 15] * x0.w + lut[(word >> 16) & 15] * x1.x + lut[(word >> 20) & 15] * x1.y +
+           lut[(word >> 24) & 15] * x1.z + lut[word >> 28] * x1.w;
+}
+
+// y[j] = W[ids[j]] x[j] for j < k (kernels.metal:1816-1880): grid (row blocks, k).
+__global__ void __launch_bounds__(kMoeWarps * 32) gemv_mxfp4_selected_kernel(
+    const uint8_t *__restrict__ elements, const uint8_t *__restrict__ scales, const uint32_t *__restrict__ ids,
+    const float *__restrict__ x, float *__restrict__ y, uint32_t rows, uint32_t cols, uint32_t x_stride,
+    uint32_t matrices) {
+    __shared__ float lut[16];   // 16 words, 16 banks: any mix of codes in a warp is one access
+    if (threadIdx.x < 16) {
+        const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+        lut[threadIdx.x] = (threadIdx.x & 8) ? -mag[threadIdx.x & 7] : mag[threadIdx.x & 7];
+    }
+    __syncthreads();
+    const uint32_t j = blockIdx.y, lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * kMoeWarps + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    // the reference trusts `ids` (written by topk_softmax over `matrices` logits); a stray index
+    // is clamped here rather than read out of bounds
+    const size_t matrix = min(ids[j], matrices - 1);
+    const uint32_t blocks = cols / 32;
+    const uint4 *e4 = reinterpret_cast<const uint4 *>(elements + matrix * rows * (cols / 2)) + static_cast<size_t>(row) * blocks;
+    const uint8_t *s = scales + matrix * rows * blocks + static_cast<size_t>(row) * blocks;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + static_cast<size_t>(j) * x_stride);
+    float acc = 0.f;
+    for (uint32_t b = lane; b < blocks; b += 32) {
+        const uint4 q = e4[b];
+        float4 xs[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xs[i] = __ldg(x4 + 8 * b + i);
+        const float block = dot_e2m1x8(q.x, lut, xs[0], xs[1]) + dot_e2m1x8(q.y, lut, xs[2], xs[3]) +
+                            dot_e2m1x8(q.z, lut, xs[4], xs[5]) + dot_e2m1x8(q.w, lut, xs[6], xs[7]);
+        acc += block * e8m0(s[b]);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[static_cast<size_t>(j) * rows + row] = acc;
+}
+
+// out = (clamp(up + ub) + 1) * g * sigmoid(alpha g), g = min(gate + gb, limit), biases of expert
+// ids[j] (kernels.metal:1893-1912; model.rs:517-525).
+__global__ void clamped_swiglu_selected_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                               const float *__restrict__ gate_bias, const float *__restrict__ up_bias,
+                                               const uint32_t *__restrict__ ids, float *__restrict__ out, uint32_t rows,
+                                               uint32_t width, uint32_t experts, float limit, float alpha) {
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= rows * width) return;
+    const uint32_t j = gid / width, i = gid % width;
+    const size_t bias = static_cast<size_t>(min(ids[j], experts - 1)) * width + i;
+    const float g = fminf(gate[gid] + gate_bias[bias], limit);
+    const float u = fminf(fmaxf(up[gid] + up_bias[bias], -limit), limit);
+    out[gid] = (u + 1.0f) * g / (1.0f + expf(-alpha * g));
+}
+
+// h[i] += sum over j < k of weights[j] * (y[j][i] + bias[ids[j]][i]) (kernels.metal:1916-1935).
+__global__ void moe_combine_kernel(float *__restrict__ h, const float *__restrict__ y, const float *__restrict__ bias,
+                                   const uint32_t *__restrict__ ids, const float *__restrict__ weights, uint32_t width,
+                                   uint32_t k, uint32_t experts) {
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= width) return;
+    float sum = 0.f;
+    for (uint32_t j = 0; j < k; ++j)
+        sum += weights[j] * (y[static_cast<size_t>(j) * width + gid] + bias[static_cast<size_t>(min(ids[j], experts - 1)) * width + gid]);
+    h[gid] += sum;
+}
+
+}  // namespace
+
+void launch_gemv_f32(const float *w, const float *x, const float *bias, float *y, uint32_t rows, uint32_t cols,
+                     cudaStream_t stream) {
+    gemv_f32_kernel<<<(rows + kMoeWarps - 1) / kMoeWarps, kMoeWarps * 32, 0, stream>>>(w, x, bias, y, rows, cols);
+}
+void launch_topk_softmax(const float *logits, uint32_t *ids, float *weights, uint32_t n, uint32_t experts, uint32_t k,
+                         cudaStream_t stream) {
+    topk_softmax_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, ids, weights, n, experts, k);
+}
+void launch_gemv_mxfp4_selected(const uint8_t *elements, const uint8_t *scales, const uint32_t *ids, const float *x,
+                                float *y, uint32_t rows, uint32_t cols, uint32_t k, uint32_t x_stride, uint32_t matrices,
+                                cudaStream_t stream) {
+    gemv_mxfp4_selected_kernel<<<dim3((rows + kMoeWarps - 1) / kMoeWarps, k), kMoeWarps * 32, 0, stream>>>(
+        elements, scales, ids, x, y, rows, cols, x_stride, matrices);
+}
+void launch_clamped_swiglu_selected(const float *gate, const float *up, const float *gate_bias, const float *up_bias,
+                                    const uint32_t *ids, float *out, uint32_t rows, uint32_t width, uint32_t experts,
+                                    float limit, float alpha, cudaStream_t stream) {
+    const uint32_t n = rows * width;
+    clamped_swiglu_selected_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gate, up, gate_bias, up_bias, ids, out, rows, width,
+                                                                       experts, limit, alpha);
+}
+void launch_moe_combine(float *h, const float *y, const float *bias, const uint32_t *ids, const float *weights,
+                        uint32_t width, uint32_t k, uint32_t experts, cudaStream_t stream) {
+    moe_combine_kernel<<<(width + 255) / 256, 256, 0, stream>>>(h, y, bias, ids, weights, width, k, experts);
+}
+
+}  // namespace cc

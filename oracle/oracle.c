@@ -318,3 +318,105 @@ void oracle_q8_0_split(const uint8_t *blocks, long n_blocks, uint8_t *codes, uin
         memcpy(codes + 32 * b, blocks + 34 * b + 2, 32);
     }
 }
+
+/* ---- MXFP4 and the routed experts ------------------------------------------------------ */
+
+/* E2M1 code -> value: bit 3 is the sign, codes 0..7 are 0, 0.5, 1, 1.5, 2, 3, 4, 6
+ * (weights/src/mxfp4.rs:19-31). */
+float oracle_e2m1(uint8_t code) {
+    static const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    return (code & 8) ? -mag[code & 7] : mag[code & 7];
+}
+
+/* E8M0 scale byte -> 2^(byte - 127); 0xFF is NaN, 0 is the subnormal 2^-127
+ * (weights/src/mxfp4.rs:33-45). */
+float oracle_e8m0(uint8_t byte) {
+    uint32_t bits = byte == 0xff ? 0x7fc00000u : byte == 0 ? (1u << 22) : (uint32_t)byte << 23;
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* ggml's MXFP4 blocks (17 bytes: the scale, then 16 bytes whose low nibbles are elements 0-15
+ * and high nibbles elements 16-31) into the layout the products use: two elements per byte, the
+ * even one in the low nibble, row by row, and one scale byte per block
+ * (`ggml_to_ocp`, weights/src/mxfp4.rs:119-149). */
+void oracle_mxfp4_ggml_to_ocp(const uint8_t *blocks, long n_blocks, uint8_t *elements, uint8_t *scales) {
+    for (long b = 0; b < n_blocks; ++b) {
+        const uint8_t *block = blocks + 17 * b;
+        scales[b] = block[0];
+        for (int j = 0; j < 16; ++j) {
+            const int i0 = 2 * j, i1 = 2 * j + 1;
+            const uint8_t c0 = i0 < 16 ? (block[1 + i0] & 0x0f) : (block[1 + i0 - 16] >> 4);
+            const uint8_t c1 = i1 < 16 ? (block[1 + i1] & 0x0f) : (block[1 + i1 - 16] >> 4);
+            elements[16 * b + j] = (uint8_t)(c0 | (c1 << 4));
+        }
+    }
+}
+
+/* y = W x for an MXFP4 matrix: per block the E2M1 values are dotted with x, the scale applied
+ * once, everything in f64 (`Mxfp4Matrix::mul_vec`, weights/src/mxfp4.rs:273-295). */
+void oracle_mxfp4_mul_vec(const uint8_t *elements, const uint8_t *scales, long rows, long cols, const float *x, float *y) {
+    const long blocks = cols / 32;
+    for (long r = 0; r < rows; ++r) {
+        double acc = 0.0;
+        for (long b = 0; b < blocks; ++b) {
+            double block = 0.0;
+            for (int i = 0; i < 32; ++i) {
+                const uint8_t byte = elements[(r * cols + b * 32 + i) / 2];
+                const uint8_t code = (i & 1) ? (byte >> 4) : (byte & 0x0f);
+                block += (double)oracle_e2m1(code) * (double)x[b * 32 + i];
+            }
+            acc += (double)oracle_e8m0(scales[r * blocks + b]) * block;
+        }
+        y[r] = (float)acc;
+    }
+}
+
+/* The k experts a position goes to and their weights: the k highest logits (equal logits: the
+ * lower index first), softmaxed over just those (`Model::route`, gpt-oss/src/model.rs:482-497). */
+void oracle_route(const float *logits, long experts, long k, int32_t *ids, float *weights) {
+    for (long j = 0; j < k; ++j) {
+        long best = -1;
+        for (long e = 0; e < experts; ++e) {
+            int taken = 0;
+            for (long i = 0; i < j; ++i) taken |= ids[i] == e;
+            if (!taken && (best < 0 || logits[e] > logits[best])) best = e;
+        }
+        ids[j] = (int32_t)best;
+    }
+    float total = 0.0f;
+    for (long j = 0; j < k; ++j) {
+        weights[j] = expf(logits[ids[j]] - logits[ids[0]]);
+        total += weights[j];
+    }
+    for (long j = 0; j < k; ++j) weights[j] /= total;
+}
+
+/* out = sum over the routed experts of weight * (down(swiglu(gate x + gb, up x + ub)) + db)
+ * (`Model::experts`, gpt-oss/src/model.rs:505-548).  Matrices of all experts one after another in
+ * the repacked layout; biases [experts][width]. */
+void oracle_experts(const float *router_logits, long experts, long k, const float *x, long hidden, long eh,
+                    const uint8_t *gate_e, const uint8_t *gate_s, const uint8_t *up_e, const uint8_t *up_s,
+                    const uint8_t *down_e, const uint8_t *down_s, const float *gate_bias, const float *up_bias,
+                    const float *down_bias, float *out) {
+    int32_t ids[16];
+    float weights[16];
+    oracle_route(router_logits, experts, k, ids, weights);
+    float *gate = malloc(sizeof(float) * eh), *up = malloc(sizeof(float) * eh), *hid = malloc(sizeof(float) * eh);
+    float *y = malloc(sizeof(float) * hidden);
+    for (long i = 0; i < hidden; ++i) out[i] = 0.0f;
+    for (long j = 0; j < k; ++j) {
+        const long e = ids[j];
+        oracle_mxfp4_mul_vec(gate_e + e * eh * hidden / 2, gate_s + e * eh * hidden / 32, eh, hidden, x, gate);
+        oracle_mxfp4_mul_vec(up_e + e * eh * hidden / 2, up_s + e * eh * hidden / 32, eh, hidden, x, up);
+        for (long i = 0; i < eh; ++i) {
+            const float g = fminf(gate[i] + gate_bias[e * eh + i], 7.0f);
+            const float u = fminf(fmaxf(up[i] + up_bias[e * eh + i], -7.0f), 7.0f);
+            hid[i] = (u + 1.0f) * g / (1.0f + expf(-1.702f * g));
+        }
+        oracle_mxfp4_mul_vec(down_e + e * hidden * eh / 2, down_s + e * hidden * eh / 32, hidden, eh, hid, y);
+        for (long i = 0; i < hidden; ++i) out[i] += weights[j] * (y[i] + down_bias[e * hidden + i]);
+    }
+    free(gate); free(up); free(hid); free(y);
+}

@@ -58,6 +58,16 @@ def lib() -> ctypes.CDLL:
         _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
         L.oracle_q8_0_mul_vec.argtypes = [_u8p, ctypes.c_long, ctypes.c_long, _f32p, _f32p]
         L.oracle_q8_0_split.argtypes = [_u8p, ctypes.c_long, _u8p, _u8p]
+        _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+        L.oracle_e2m1.restype = ctypes.c_float
+        L.oracle_e2m1.argtypes = [ctypes.c_uint8]
+        L.oracle_e8m0.restype = ctypes.c_float
+        L.oracle_e8m0.argtypes = [ctypes.c_uint8]
+        L.oracle_mxfp4_ggml_to_ocp.argtypes = [_u8p, ctypes.c_long, _u8p, _u8p]
+        L.oracle_mxfp4_mul_vec.argtypes = [_u8p, _u8p, ctypes.c_long, ctypes.c_long, _f32p, _f32p]
+        L.oracle_route.argtypes = [_f32p, ctypes.c_long, ctypes.c_long, _i32p, _f32p]
+        L.oracle_experts.argtypes = [_f32p, ctypes.c_long, ctypes.c_long, _f32p, ctypes.c_long, ctypes.c_long,
+                                     _u8p, _u8p, _u8p, _u8p, _u8p, _u8p, _f32p, _f32p, _f32p, _f32p]
         _lib = L
     return _lib
 
@@ -92,6 +102,15 @@ def xorshift_values(seed: int, n: int) -> np.ndarray:
     out = np.zeros(n, np.float32)
     lib().oracle_xorshift_values(seed, n, out)
     return out
+
+
+def mxfp4_ggml_to_ocp(blocks: np.ndarray):
+    """`ggml_to_ocp` (weights/src/mxfp4.rs:119-149): (elements, scales) of ggml MXFP4 blocks."""
+    blocks = np.ascontiguousarray(blocks, np.uint8).reshape(-1)
+    n = blocks.size // 17
+    elements, scales = np.zeros(n * 16, np.uint8), np.zeros(n, np.uint8)
+    lib().oracle_mxfp4_ggml_to_ocp(blocks, n, elements, scales)
+    return elements, scales
 
 
 def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:

@@ -42,8 +42,10 @@ def load(reference_root: str):
     tensors = {t.name: np.array(dequantize(t.data, t.tensor_type), np.float32) for t in reader.tensors}
     # the attention projections also as they are stored: ggml Q8_0 blocks, row after row
     for t in reader.tensors:
-        if t.tensor_type == gguf.GGMLQuantizationType.Q8_0 and ".attn_" in t.name:
+        if t.tensor_type == gguf.GGMLQuantizationType.Q8_0:
             tensors[t.name + ":q8_0"] = np.ascontiguousarray(t.data, np.uint8).reshape(-1)
+        if t.tensor_type == gguf.GGMLQuantizationType.MXFP4:
+            tensors[t.name + ":mxfp4"] = np.ascontiguousarray(t.data, np.uint8).reshape(-1)
     with open(os.path.join(d, "oracle.json")) as fh:
         ids = json.load(fh)["ids"]
     logits = np.fromfile(os.path.join(d, "logits.f32"), np.float32)
@@ -129,6 +131,8 @@ def replay(meta, T, ids, mutation: str | None = None, record: dict | None = None
                 record.setdefault(f"l{l}_h_att", []).append(h.copy())
                 record.setdefault(f"l{l}_x_ffn", []).append(x.copy())
             h = h + experts(T, l, x, used)
+            if record is not None:
+                record.setdefault(f"l{l}_h_out", []).append(h.copy())
         x = rms_norm(h, T["output_norm.weight"], eps)
         all_logits.append((T["output.weight"] @ x).astype(np.float32))
     if record is not None:
@@ -169,7 +173,7 @@ def main():
     }))
     # the block-level vectors (residual stream in and out of the attention half of each layer, the
     # Q8_0 projections as stored) go to a file of their own
-    block = {k: out.pop(k) for k in [k for k in out if k.endswith(("_h_in", "_h_att", "_x_ffn"))]}
+    block = {k: out.pop(k) for k in [k for k in out if k.endswith(("_h_in", "_h_att", "_x_ffn", "_h_out"))]}
     for l in range(meta["gpt-oss.block_count"]):
         for name in ("attn_q", "attn_k", "attn_v", "attn_output"):
             block[f"l{l}_{name}_q8_0"] = T[f"blk.{l}.{name}.weight:q8_0"]
@@ -177,13 +181,27 @@ def main():
         block[f"l{l}_attn_norm"] = T[f"blk.{l}.attn_norm.weight"].astype(np.float32)
         block[f"l{l}_ffn_norm"] = T[f"blk.{l}.post_attention_norm.weight"].astype(np.float32)
         block[f"l{l}_sinks"] = out[f"l{l}_sinks"]
+        # the experts as stored: router (f32), ggml MXFP4 blocks of all experts, biases
+        block[f"l{l}_router"] = T[f"blk.{l}.ffn_gate_inp.weight"].astype(np.float32)
+        block[f"l{l}_router_bias"] = T[f"blk.{l}.ffn_gate_inp.bias"].astype(np.float32)
+        for name in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
+            block[f"l{l}_{name}_mxfp4"] = T[f"blk.{l}.{name}.weight:mxfp4"]
+            block[f"l{l}_{name}_bias"] = T[f"blk.{l}.{name}.bias"].astype(np.float32)
+    # what surrounds the layers: embedding rows of the prompt's tokens (widened), the final norm,
+    # the output matrix as stored, and the logits the reference's fixture holds
+    block["embedded"] = np.stack([T["token_embd.weight"][t] for t in ids]).astype(np.float32)
+    block["output_norm"] = T["output_norm.weight"].astype(np.float32)
+    block["output_q8_0"] = T["output.weight:q8_0"]
+    block["logits"] = want.astype(np.float32)
     block["meta"] = np.array(json.dumps({
         "layers": meta["gpt-oss.block_count"], "hidden": int(T["token_embd.weight"].shape[1]),
         "heads": meta["gpt-oss.attention.head_count"], "kv_heads": meta["gpt-oss.attention.head_count_kv"],
         "dim": meta["gpt-oss.attention.key_length"], "window": meta["gpt-oss.attention.sliding_window"],
         "eps": float(meta["gpt-oss.attention.layer_norm_rms_epsilon"]),
         "theta": meta["gpt-oss.rope.freq_base"], "factor": meta["gpt-oss.rope.scaling.factor"],
-        "original_context": meta["gpt-oss.rope.scaling.original_context_length"], "positions": len(ids)}))
+        "original_context": meta["gpt-oss.rope.scaling.original_context_length"], "positions": len(ids),
+        "experts": meta["gpt-oss.expert_count"], "experts_used": meta["gpt-oss.expert_used_count"],
+        "expert_hidden": meta["gpt-oss.feed_forward_length"], "vocab": int(want.shape[1])}))
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tiny_attention.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path} ({os.path.getsize(path)} bytes)")

@@ -1,0 +1,147 @@
+"""The routed-experts kernels through the C ABI, the way the reference tests them
+(metal-compute/tests/q8_0_and_gpt_oss_glue.rs:285-470: a router with a tie, MXFP4 experts, the
+clamped SwiGLU with per-expert biases, the weighted sum into the residual, all against float64),
+and the whole tiny fixture decoded on the GPU one token at a time against the logits the
+reference's fixture holds (gpt-oss/tests/gpu_oracle.rs:76-145, tolerance 2e-3)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from loadngo_b200 import compute
+from loadngo_b200.compute import Slice
+from loadngo_b200.gpt_oss import Config, GpuModel
+from oracle import oracle
+from tests.helpers import xorshift_values as values
+
+pytestmark = pytest.mark.gpu
+BLOCK_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_block.npz")
+E2M1 = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6], np.float64)
+
+
+def mxfp4(rng, matrices, rows, cols):
+    """Random MXFP4 matrices in the repacked layout, and every element's value."""
+    codes = rng.integers(0, 16, (matrices, rows, cols), dtype=np.uint8)
+    scales = rng.integers(118, 130, (matrices, rows, cols // 32), dtype=np.uint8)
+    elements = (codes[..., 0::2] | (codes[..., 1::2] << 4)).astype(np.uint8)
+    w = E2M1[codes] * np.repeat(2.0 ** (scales.astype(np.float64) - 127), 32, axis=-1)
+    return elements.reshape(-1), scales.reshape(-1), w
+
+
+def test_routing_picks_runs_and_combines_experts(gpu):
+    rng = np.random.default_rng(9)
+    experts, k, hidden, width = 8, 3, 64, 96
+    router = values(21, experts * hidden).reshape(experts, hidden)
+    router_bias = values(22, experts)
+    x = values(23, hidden)
+    dot = lambda e: np.float32(np.sum(router[e] * x, dtype=np.float32))
+    router_bias[5] = router_bias[2] + dot(2) - dot(5)             # a tie between experts 2 and 5
+    gate, up, down = mxfp4(rng, experts, width, hidden), mxfp4(rng, experts, width, hidden), mxfp4(rng, experts, hidden, width)
+    gate_bias = values(31, experts * width) * np.float32(3.0)
+    up_bias, down_bias, h = values(32, experts * width), values(33, experts * hidden), values(34, hidden)
+    up_ = gpu.upload
+    bufs = [up_(router), up_(router_bias), up_(x), gpu.buffer(experts * 4), gpu.buffer(64), gpu.buffer(64),
+            up_(gate[0]), up_(gate[1]), up_(up[0]), up_(up[1]), up_(down[0]), up_(down[1]), gpu.buffer(k * width * 4),
+            gpu.buffer(k * width * 4), gpu.buffer(k * width * 4), gpu.buffer(k * hidden * 4), up_(gate_bias), up_(up_bias),
+            up_(down_bias), up_(h)]
+    batch = gpu.batch(bufs)
+    f = lambda b, n: Slice(b, 0, n * 4)
+    raw = lambda b, n: Slice(b, 0, n)
+    batch.gemv_f32((f(0, router.size), f(1, experts)), f(2, hidden), f(3, experts), experts, hidden)
+    batch.topk_softmax(f(3, experts), (f(4, k), f(5, k)), 1, (experts, k))
+    ids = f(4, k)
+    batch.gemv_mxfp4_selected((raw(6, gate[0].size), raw(7, gate[1].size), experts), ids, (f(2, hidden), 0), f(12, k * width),
+                              (width, hidden), k)
+    batch.gemv_mxfp4_selected((raw(8, up[0].size), raw(9, up[1].size), experts), ids, (f(2, hidden), 0), f(13, k * width),
+                              (width, hidden), k)
+    batch.clamped_swiglu_selected((f(12, k * width), f(13, k * width)), (f(16, gate_bias.size), f(17, up_bias.size), experts),
+                                  ids, f(14, k * width), (k, width), (7.0, 1.702))
+    batch.gemv_mxfp4_selected((raw(10, down[0].size), raw(11, down[1].size), experts), ids, (f(14, k * width), width),
+                              f(15, k * hidden), (hidden, width), k)
+    batch.moe_combine(f(19, hidden), (f(15, k * hidden), f(18, down_bias.size), experts), (ids, f(5, k)), (k, hidden))
+    done = batch.run()
+    assert not isinstance(done.gpu_time, Exception), done.gpu_time
+    # the CPU's choice: highest logits, the lower index first on ties
+    logits = np.array([dot(e) + router_bias[e] for e in range(experts)], np.float32)
+    got_logits = bufs[3].as_f32()[:experts]
+    assert np.abs(got_logits - logits).max() < 1e-5
+    order = sorted(range(experts), key=lambda e: (-got_logits[e], e))[:k]
+    got_ids = bufs[4].view(np.uint32)[:k].tolist()
+    assert got_ids == order, (got_ids, order, got_logits)
+    if abs(float(got_logits[2]) - float(got_logits[5])) == 0.0 and 2 in order and 5 in order:
+        assert order.index(2) < order.index(5)
+    exps = np.exp(got_logits[order].astype(np.float64) - float(got_logits[order[0]]))
+    assert np.abs(bufs[5].as_f32()[:k] - exps / exps.sum()).max() < 1e-6
+    want = h.astype(np.float64)
+    for j, e in enumerate(order):
+        g = np.minimum(gate[2][e] @ x.astype(np.float64) + gate_bias[e * width:(e + 1) * width], 7.0)
+        u = np.clip(up[2][e] @ x.astype(np.float64) + up_bias[e * width:(e + 1) * width], -7.0, 7.0)
+        hid = ((u + 1.0) * g / (1.0 + np.exp(-1.702 * g))).astype(np.float32)
+        y = down[2][e] @ hid.astype(np.float64)
+        want = want + exps[j] / exps.sum() * (y + down_bias[e * hidden:(e + 1) * hidden])
+    got = bufs[19].as_f32()[:hidden]
+    assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max()), np.abs(got - want).max()
+    for b in bufs:
+        b.free()
+
+
+def test_moe_entries_reject_what_the_reference_rejects(gpu):
+    bufs = [gpu.buffer(1 << 14) for _ in range(4)]
+    batch = gpu.batch(bufs)
+    S = Slice
+    with pytest.raises(compute.DispatchError):
+        batch.gemv_f32((S(0, 0, 8 * 6 * 4), None), S(1, 0, 6 * 4), S(2, 0, 8 * 4), 8, 6)          # cols % 4
+    with pytest.raises(compute.DispatchError):
+        batch.topk_softmax(S(0, 0, 8 * 4), (S(1, 0, 17 * 4), S(2, 0, 17 * 4)), 1, (8, 17))        # k > 16
+    with pytest.raises(compute.DispatchError):
+        batch.topk_softmax(S(0, 0, 2 * 4), (S(1, 0, 3 * 4), S(2, 0, 3 * 4)), 1, (2, 3))           # k > experts
+    with pytest.raises(compute.DispatchError):
+        batch.gemv_mxfp4_selected((S(0, 0, 4 * 8 * 48 // 2), S(1, 0, 4 * 8 * 48 // 32), 4), S(2, 0, 8), (S(3, 0, 48 * 4), 0),
+                                  S(3, 1024, 2 * 8 * 4), (8, 48), 2)                               # cols % 32
+    with pytest.raises(compute.DispatchError):
+        batch.moe_combine(S(0, 0, 64 * 4), (S(0, 0, 2 * 64 * 4), S(1, 0, 4 * 64 * 4), 4), (S(2, 0, 8), S(2, 64, 8)), (2, 64))  # h overlaps y
+    batch.drop()
+    for b in bufs:
+        b.free()
+
+
+def test_tiny_fixture_decoded_whole_on_the_gpu():
+    """All 40 tokens of the reference's fixture, one submission each, every layer's attention and
+    routed experts and the output head on the GPU from the weights as the GGUF stores them: the
+    logits match the fixture's (transformers' fp32 eager output) within the reference's own 2e-3;
+    then a rewind and a second pass over the tail give the same logits again."""
+    g = np.load(BLOCK_GOLDEN)
+    meta = json.loads(str(g["meta"]))
+    cfg = Config(layers=meta["layers"], hidden=meta["hidden"], heads=meta["heads"], kv_heads=meta["kv_heads"],
+                 head_dim=meta["dim"], window=meta["window"], eps=meta["eps"], experts=meta["experts"],
+                 experts_used=meta["experts_used"], expert_hidden=meta["expert_hidden"], vocab=meta["vocab"],
+                 theta=meta["theta"], factor=meta["factor"], original_context=float(meta["original_context"]))
+    tensors = {"output.weight": g["output_q8_0"], "output_norm.weight": g["output_norm"]}
+    for l in range(cfg.layers):
+        for name in ("attn_q", "attn_k", "attn_v", "attn_output"):
+            tensors[f"blk.{l}.{name}.weight"] = g[f"l{l}_{name}_q8_0"]
+            tensors[f"blk.{l}.{name}.bias"] = g[f"l{l}_{name}_bias"]
+        tensors[f"blk.{l}.attn_norm.weight"] = g[f"l{l}_attn_norm"]
+        tensors[f"blk.{l}.post_attention_norm.weight"] = g[f"l{l}_ffn_norm"]
+        tensors[f"blk.{l}.attn_sinks.weight"] = g[f"l{l}_sinks"]
+        tensors[f"blk.{l}.ffn_gate_inp.weight"] = g[f"l{l}_router"]
+        tensors[f"blk.{l}.ffn_gate_inp.bias"] = g[f"l{l}_router_bias"]
+        for name in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
+            tensors[f"blk.{l}.{name}.weight"] = g[f"l{l}_{name}_mxfp4"]
+            tensors[f"blk.{l}.{name}.bias"] = g[f"l{l}_{name}_bias"]
+    gpu = compute.Gpu(0)
+    model = GpuModel(gpu, cfg, tensors, capacity=meta["positions"])
+    worst = 0.0
+    for p in range(meta["positions"]):
+        logits = model.step(g["embedded"][p])
+        worst = max(worst, float(np.abs(logits - g["logits"][p]).max()))
+    print(f"\ntiny fixture on the GPU: worst logit error over {meta['positions']} positions = {worst:.3e} (tolerance 2e-3)")
+    assert worst < 2e-3
+    # rewind five positions (inside what the sliding rings still hold) and decode them again
+    model.truncate(meta["positions"] - 5)
+    for p in range(meta["positions"] - 5, meta["positions"]):
+        logits = model.step(g["embedded"][p])
+        assert float(np.abs(logits - g["logits"][p]).max()) < 2e-3
+    model.free()
+    gpu.free()

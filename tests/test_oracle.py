@@ -191,3 +191,28 @@ def test_q8_0_product_reproduces_the_tiny_fixtures_projections():
                 oracle.lib().oracle_q8_0_mul_vec(np.ascontiguousarray(blk[f"l{l}_{name}_q8_0"]), want.size, hidden, x, y)
                 y += blk[f"l{l}_{name}_bias"]
                 assert np.abs(y - want).max() < 2e-5, (l, p, name)
+
+
+def test_experts_reproduce_the_tiny_fixtures_residual_stream():
+    """The oracle's routed experts (MXFP4 decoding and repacking, routing with ties to the lower
+    index, clamped SwiGLU, weighted sum: gpt-oss/src/model.rs:480-548) on the fixture's stored
+    blocks give the residual stream that the pinned replay computed with the `gguf` package's own
+    dequantisation of the same tensors."""
+    import json
+    import os
+    blk = np.load(os.path.join(os.path.dirname(__file__), "golden", "tiny_block.npz"))
+    meta = json.loads(str(blk["meta"]))
+    hidden, eh, experts, k = meta["hidden"], meta["expert_hidden"], meta["experts"], meta["experts_used"]
+    assert oracle.lib().oracle_e2m1(0b1101) == -3.0 and oracle.lib().oracle_e8m0(128) == 2.0
+    for l in range(meta["layers"]):
+        mats = {n: oracle.mxfp4_ggml_to_ocp(blk[f"l{l}_{n}_mxfp4"]) for n in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps")}
+        for p in (0, 13, meta["positions"] - 1):
+            x = np.ascontiguousarray(blk[f"l{l}_x_ffn"][p])
+            logits = (blk[f"l{l}_router"].astype(np.float64) @ x + blk[f"l{l}_router_bias"]).astype(np.float32)
+            out = np.zeros(hidden, np.float32)
+            oracle.lib().oracle_experts(logits, experts, k, x, hidden, eh, *mats["ffn_gate_exps"], *mats["ffn_up_exps"],
+                                        *mats["ffn_down_exps"], np.ascontiguousarray(blk[f"l{l}_ffn_gate_exps_bias"]).reshape(-1),
+                                        np.ascontiguousarray(blk[f"l{l}_ffn_up_exps_bias"]).reshape(-1),
+                                        np.ascontiguousarray(blk[f"l{l}_ffn_down_exps_bias"]).reshape(-1), out)
+            want = blk[f"l{l}_h_out"][p] - blk[f"l{l}_h_att"][p]
+            assert np.abs(out - want).max() < 5e-5, (l, p, np.abs(out - want).max())
