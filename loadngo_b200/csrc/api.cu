@@ -104,7 +104,8 @@ int make_q_map(CUtensorMap *map, const void *q, uint64_t tokens, uint32_t heads)
 uint32_t div_up(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 
 // Pages a sequence of `max_seq_len` keys can show one query, and the split policy: enough
-// CTAs for several waves over 148 SMs x 3 resident CTAs, splits no shorter than 16 pages.
+// CTAs for several waves over 148 SMs x 4 resident CTAs if every sequence had the longest length
+// (a ragged batch then still fills two to three), splits no shorter than 16 pages.
 uint32_t visible_pages(uint32_t max_seq_len, uint32_t window) {
     if (max_seq_len == 0) return 1;
     if (window != 0 && max_seq_len > window) {

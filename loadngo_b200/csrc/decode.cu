@@ -11,7 +11,7 @@
 // KV head eight times; here the 8 query heads that share a KV head are one MMA tile, so the
 // cache is read once.  Long sequences are cut into splits of `pages_per_split` pages; a CTA
 // owns one (sequence, KV head, split).  Its 4 warps each stream their own pages (16 keys,
-// one 4 KiB K+V tile) from HBM with TMA into a private 4-stage ring of shared memory
+// one 4 KiB K+V tile) from HBM with TMA into a private 3-stage ring of shared memory
 // (128-byte swizzle), so no warp ever waits for another inside the loop.  QK^T and PV run on
 // mma.sync m16n8k16: the 16 rows are the 8 heads' bf16 "hi" parts and their "lo" remainders,
 // (q = hi + lo, p = hi + lo), which costs nothing - the rows would be padding - and keeps the
@@ -28,14 +28,14 @@ namespace cc {
 namespace {
 
 constexpr int kWarps = 4;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kThreads = kWarps * 32;
-constexpr int kWarpBytes = kStages * kTileBytes;                     // 16 KiB
+constexpr int kWarpBytes = kStages * kTileBytes;                     // 12 KiB
 constexpr int kSmemBytes = kWarps * kWarpBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 
-__global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_constant__ DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -73,12 +73,20 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_consta
     }
     __syncwarp();
 
+    // This warp's block-table entries, fetched up front by all lanes at once (two per lane cover
+    // the 64 pages a warp can own): the TMA copies of a fresh CTA then wait for one round trip to
+    // the table, not for one per pipeline stage.
     const int32_t *table_row = p.block_table + static_cast<size_t>(b) * p.max_pages;
-    auto issue = [&](int it) {
+    auto table_entry = [&](int it) -> int32_t {
         const int lp = p0 + warp + it * kWarps;
         uint32_t idx = static_cast<uint32_t>(lp);
         if (p.ring_pages) idx %= p.ring_pages;
-        int32_t page = idx < p.max_pages ? table_row[idx] : -1;
+        return (it < count && idx < p.max_pages) ? table_row[idx] : -1;
+    };
+    const int32_t entry0 = table_entry(lane), entry1 = table_entry(lane + 32);
+    auto issue = [&](int it) {   // called by the whole warp
+        int32_t page = it < 64 ? __shfl_sync(0xffffffffu, it < 32 ? entry0 : entry1, it & 31) : table_entry(it);
+        if (lane != 0) return;
         if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages) {
             raise_status(p.status, kStatusBadPage);
             page = 0;  // still complete the copy so the pipeline drains; the status marks the result invalid
@@ -88,9 +96,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_consta
         tma_load_2d(my_tiles + stage * kTileBytes, &p.pool_map, 0,
                     (page * static_cast<int>(p.kv_heads) + g) * kTileRows, &my_bars[stage]);
     };
-    if (lane == 0) {
-        for (int s = 0; s < kStages && s < count; ++s) issue(s);
-    }
+    for (int s = 0; s < kStages && s < count; ++s) issue(s);
 
     // Query fragments: row r (0-7) = head r "hi", row r + 8 = the same head's "lo".
     const int hr = lane >> 2, tq = lane & 3;
@@ -140,7 +146,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const __grid_consta
             ldmatrix_x4_trans(tile + v_row * 128 + ((chunk ^ r8) << 4), vb[c][0], vb[c][1], vb[c][2], vb[c][3]);
         }
         __syncwarp();
-        if (lane == 0 && it + kStages < count) issue(it + kStages);
+        if (it + kStages < count) issue(it + kStages);
 
         // S = Q K^T for 16 keys: rows hi and lo add up to the full-precision dot.
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
