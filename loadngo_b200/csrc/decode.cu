@@ -303,11 +303,8 @@ size_t decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_spl
 }
 
 void launch_decode(const DecodeParams &p, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        configured = true;
-    }
+    // per device, so set on every launch (a process may drive more than one GPU); it is cheap
+    cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     dim3 grid(p.max_splits, p.kv_heads, p.seqs);
     decode_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
 }

@@ -400,6 +400,10 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                             PROF_FAIL(ok, 4, n);
                             q_ready[g] = true;
                         }
+                        const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + sl * 2 * kPlaneBytes, 16, 1024);
+                        const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
+                        const uint32_t d = tmem + static_cast<uint32_t>(n % kSBufs) * kTileK;
+                        uint64_t *full_bar = &bars->s_full[n % kSBufs];
                         // S(n) goes where P(n - 3) was.  The tensor pipe runs what it is given in order,
                         // so that product only has to have been issued (not finished) before these scores
                         // are: the fences on both sides of the barrier order the two threads' instructions.
@@ -410,16 +414,13 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                         PROF_FAIL(ok, 5, n);
                         if (!ok) break;
                         tc_fence_after();
-                        const uint64_t qhi_desc = smem_desc_sw128(smem_base + kOffQ + sl * 2 * kPlaneBytes, 16, 1024);
-                        const uint64_t qlo_desc = qhi_desc + (kPlaneBytes >> 4);
-                        const uint32_t d = tmem + static_cast<uint32_t>(n % kSBufs) * kTileK;
                         TRACE2(2, n);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qhi_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks > 0);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) umma_bf16(d, qlo_desc + ks * 2, k_desc + ks * 2, idesc_qk, true);
                         TRACE2(0, n);
-                        umma_commit(&bars->s_full[n % kSBufs]);
+                        umma_commit(full_bar);
                         if (kt == it.hi[g]) umma_commit(&bars->q_empty[sl]);   // all scores of this query tile are issued
                         ++n;
                     }
@@ -449,23 +450,27 @@ __global__ void __launch_bounds__(kThreadsPrefill, 1) prefill_kernel(const __gri
                         // the first product of an item overwrites O: the previous item's rows must be out
                         if (first[g] && items_of[g] > 0) ok = mbar_wait(&bars->o_free[g], (items_of[g] - 1) & 1);
                         PROF_FAIL(ok, 6, n);
-                        PROF_BEGIN(t_pf);
-                        if (ok) ok = mbar_wait(&bars->p_full[n % kSBufs], (n / kSBufs) & 1);
-                        PROF_END(14, t_pf);
-                        PROF_FAIL(ok, 7, n);
+                        // everything that does not need P first: what follows the wait for P is on
+                        // the critical path of the job after next
                         if (ok) ok = mbar_wait(&bars->kv_full[stage], (gt / kStagesKV) & 1);   // long since there
-                        if (!ok) break;
-                        tc_fence_after();
                         // P comes from tensor memory: 16 keys of a k-step are 8 columns of packed bf16 pairs;
                         // keys 0-63 sit in columns 0-31 of the buffer, keys 64-127 in columns 64-95
                         const uint32_t p_tmem = tmem + static_cast<uint32_t>(n % kSBufs) * kTileK;
                         const uint32_t o_tmem = tmem + kColO + static_cast<uint32_t>(g) * kHeadDim;
+                        uint64_t *done_bar = &bars->pv_done[n % kPvRing], *issued_bar = &bars->pv_issued[n % kPvRing];
+                        const bool fresh = first[g];
+                        PROF_BEGIN(t_pf);
+                        if (ok) ok = mbar_wait(&bars->p_full[n % kSBufs], (n / kSBufs) & 1);
+                        PROF_END(14, t_pf);
+                        PROF_FAIL(ok, 7, n);
+                        if (!ok) break;
+                        tc_fence_after();
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks)
-                            umma_bf16_ts(o_tmem, p_tmem + (ks >> 2) * 64 + (ks & 3) * 8, v_desc + ks * (2048 >> 4), idesc_pv, !first[g] || ks > 0);
-                        umma_commit(&bars->pv_done[n % kPvRing]);
+                            umma_bf16_ts(o_tmem, p_tmem + (ks >> 2) * 64 + (ks & 3) * 8, v_desc + ks * (2048 >> 4), idesc_pv, !fresh || ks > 0);
+                        umma_commit(done_bar);
                         tc_fence_before();
-                        mbar_arrive(&bars->pv_issued[n % kPvRing]);
+                        mbar_arrive(issued_bar);
                         TRACE2(1, n);
                         first[g] = false;
                         ++n;
