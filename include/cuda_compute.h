@@ -342,6 +342,18 @@ int cc_batch_gemm_q8_0_tiled(cc_batch *batch, cc_slice codes, cc_slice scales, c
  * clamped_swiglu_selected (apple.rs:2126-2160): out = (clamp(up + ub, -limit, limit) + 1) * g *
  *   sigmoid(alpha g), g = min(gate + gb, limit), biases rows ids[j] of [experts][width].
  * moe_combine (apple.rs:2164-2191): h += sum_j weights[j] * (y[j] + bias[ids[j]]). */
+/* Batch::gemv_mxfp4, gemm_mxfp4, gemm_mxfp4_tiled (apple.rs:964-1096): y[p] = W x[p] for one
+ * rows x cols MXFP4 matrix (layout as above) and n positions; strides and alignment as the Q8_0
+ * products; the tiled form also needs rows % 64 == 0 and n % 32 == 0.  Batch::clamped_swiglu
+ * (apple.rs:1961-1995): as the selected form with one bias row [width] for all rows. */
+int cc_batch_gemv_mxfp4(cc_batch *batch, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                        uint64_t cols);
+int cc_batch_gemm_mxfp4(cc_batch *batch, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                        uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride);
+int cc_batch_gemm_mxfp4_tiled(cc_batch *batch, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                              uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride);
+int cc_batch_clamped_swiglu(cc_batch *batch, cc_slice gate, cc_slice up, cc_slice gate_bias, cc_slice up_bias, cc_slice out,
+                            uint64_t rows, uint64_t width, float limit, float alpha);
 int cc_batch_gemv_f32(cc_batch *batch, cc_slice w, const cc_slice *bias, cc_slice x, cc_slice y, uint64_t rows,
                       uint64_t cols);
 int cc_batch_topk_softmax(cc_batch *batch, cc_slice logits, cc_slice ids, cc_slice weights, uint64_t n, uint64_t experts,

@@ -173,6 +173,13 @@ SYMBOLS = {
     "cc_batch_copy_rows": (c_int, [c_void_p, Slice, c_uint64, Slice, c_uint64, c_uint64, c_uint64]),
     "cc_batch_rmsnorm_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64, c_float]),
     "cc_batch_add_rows": (c_int, [c_void_p, Slice, Slice, c_uint64, c_uint64, c_uint64]),
+    "cc_batch_gemv_mxfp4": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64]),
+    "cc_batch_gemm_mxfp4": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64, c_uint64,
+                                    c_uint64]),
+    "cc_batch_gemm_mxfp4_tiled": (c_int, [c_void_p, Slice, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64, c_uint64,
+                                          c_uint64]),
+    "cc_batch_clamped_swiglu": (c_int, [c_void_p, Slice, Slice, Slice, Slice, Slice, c_uint64, c_uint64, c_float,
+                                        c_float]),
     "cc_batch_gemv_f32": (c_int, [c_void_p, Slice, POINTER(Slice), Slice, Slice, c_uint64, c_uint64]),
     "cc_batch_topk_softmax": (c_int, [c_void_p, Slice, Slice, Slice, c_uint64, c_uint64, c_uint64]),
     "cc_batch_gemv_mxfp4_selected": (c_int, [c_void_p, Slice, Slice, c_uint64, Slice, Slice, c_uint64, Slice, c_uint64,
@@ -416,6 +423,20 @@ class Batch:
     def add_rows(self, dst: Slice, src, rows: int, width: int) -> None:
         s, ss = src
         check(lib().cc_batch_add_rows(self._h, dst, s, ss, rows, width))
+
+    def gemv_mxfp4(self, elements: Slice, scales: Slice, x: Slice, y: Slice, rows: int, cols: int) -> None:
+        check(lib().cc_batch_gemv_mxfp4(self._h, elements, scales, x, y, rows, cols))
+
+    def gemm_mxfp4(self, elements: Slice, scales: Slice, x: Slice, y: Slice, rows: int, cols: int, n: int, strides) -> None:
+        check(lib().cc_batch_gemm_mxfp4(self._h, elements, scales, x, y, rows, cols, n, strides[0], strides[1]))
+
+    def gemm_mxfp4_tiled(self, elements: Slice, scales: Slice, x: Slice, y: Slice, rows: int, cols: int, n: int,
+                         strides) -> None:
+        check(lib().cc_batch_gemm_mxfp4_tiled(self._h, elements, scales, x, y, rows, cols, n, strides[0], strides[1]))
+
+    def clamped_swiglu(self, gate_up, biases, out: Slice, rows: int, width: int, limit_alpha) -> None:
+        (gate, up), (gb, ub), (limit, alpha) = gate_up, biases, limit_alpha
+        check(lib().cc_batch_clamped_swiglu(self._h, gate, up, gb, ub, out, rows, width, limit, alpha))
 
     def gemv_f32(self, w_bias, x: Slice, y: Slice, rows: int, cols: int) -> None:
         """`Batch::gemv_f32` (apple.rs:2000-2039); `w_bias` = (w, bias or None)."""

@@ -1007,6 +1007,81 @@ extern "C" int cc_batch_moe_combine(cc_batch *b, cc_slice h, cc_slice y, cc_slic
     return CC_OK;
 }
 
+namespace {
+
+// gemv_mxfp4, gemm_mxfp4, gemm_mxfp4_tiled share their checks (apple.rs:964-1096) and their kernel.
+int record_mxfp4(cc_batch *b, const char *what, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                 uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride) {
+    if (!b) return fail(CC_DISPATCH, "%s: null batch", what);
+    if (rows == 0 || cols == 0) return fail(CC_DISPATCH, "%s: empty matrix", what);
+    if (cols % 32 != 0) return fail(CC_DISPATCH, "MXFP4 rows of %llu are not whole blocks", (unsigned long long)cols);
+    if (n == 0 || x_stride < cols || y_stride < rows || x_stride % 4 != 0)
+        return fail(CC_DISPATCH, "%llu positions of %llu x %llu with strides %llu/%llu", (unsigned long long)n,
+                    (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)x_stride,
+                    (unsigned long long)y_stride);
+    uint32_t r, c, nn, xs, ys, tmp;
+    if (narrow(rows, &r) || narrow(cols, &c) || narrow(n, &nn) || narrow(x_stride, &xs) || narrow(y_stride, &ys) ||
+        narrow(rows * cols, &tmp))
+        return CC_DISPATCH;
+    uint8_t *pe, *ps, *px, *py;
+    if (int rc = check(b, "elements", elements, rows * cols / 2, 16, &pe)) return rc;
+    if (int rc = check(b, "scales", scales, rows * cols / 32, 1, &ps)) return rc;
+    if (int rc = check(b, "x", x, ((n - 1) * x_stride + cols) * 4, 16, &px)) return rc;
+    if (int rc = check(b, "y", y, ((n - 1) * y_stride + rows) * 4, 4, &py)) return rc;
+    if (int rc = check_output(b, y, {&elements, &scales, &x})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_mxfp4(pe, ps, reinterpret_cast<const float *>(px), reinterpret_cast<float *>(py), r, c, nn, xs, ys, s);
+        return CC_OK;
+    });
+    wrote(b, y);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+}  // namespace
+
+extern "C" int cc_batch_gemv_mxfp4(cc_batch *b, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                                   uint64_t cols) {
+    return record_mxfp4(b, "gemv_mxfp4", elements, scales, x, y, rows, cols, 1, cols, rows);
+}
+
+extern "C" int cc_batch_gemm_mxfp4(cc_batch *b, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y, uint64_t rows,
+                                   uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride) {
+    return record_mxfp4(b, "gemm_mxfp4", elements, scales, x, y, rows, cols, n, x_stride, y_stride);
+}
+
+extern "C" int cc_batch_gemm_mxfp4_tiled(cc_batch *b, cc_slice elements, cc_slice scales, cc_slice x, cc_slice y,
+                                         uint64_t rows, uint64_t cols, uint64_t n, uint64_t x_stride, uint64_t y_stride) {
+    if (rows % 64 != 0 || cols % 32 != 0 || n % 32 != 0)
+        return fail(CC_DISPATCH, "tiled MXFP4 product needs rows %% 64, cols %% 32 and n %% 32 == 0: %llu x %llu, n %llu",
+                    (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)n);
+    return record_mxfp4(b, "gemm_mxfp4_tiled", elements, scales, x, y, rows, cols, n, x_stride, y_stride);
+}
+
+extern "C" int cc_batch_clamped_swiglu(cc_batch *b, cc_slice gate, cc_slice up, cc_slice gate_bias, cc_slice up_bias,
+                                       cc_slice out, uint64_t rows, uint64_t width, float limit, float alpha) {
+    if (!b) return fail(CC_DISPATCH, "clamped_swiglu: null batch");
+    if (rows == 0 || width == 0) return fail(CC_DISPATCH, "empty clamped_swiglu");
+    uint32_t r, w, tmp;
+    if (narrow(rows, &r) || narrow(width, &w) || narrow(rows * width, &tmp)) return CC_DISPATCH;
+    uint8_t *pg, *pu, *pgb, *pub, *po;
+    if (int rc = check(b, "gate", gate, rows * width * 4, 4, &pg)) return rc;
+    if (int rc = check(b, "up", up, rows * width * 4, 4, &pu)) return rc;
+    if (int rc = check(b, "out", out, rows * width * 4, 4, &po)) return rc;
+    if (int rc = check(b, "gate_bias", gate_bias, width * 4, 4, &pgb)) return rc;
+    if (int rc = check(b, "up_bias", up_bias, width * 4, 4, &pub)) return rc;
+    if (int rc = check_output(b, out, {&gate, &up, &gate_bias, &up_bias})) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_clamped_swiglu(reinterpret_cast<const float *>(pg), reinterpret_cast<const float *>(pu),
+                                  reinterpret_cast<const float *>(pgb), reinterpret_cast<const float *>(pub),
+                                  reinterpret_cast<float *>(po), r, w, limit, alpha, s);
+        return CC_OK;
+    });
+    wrote(b, out);
+    ++b->dispatches;
+    return CC_OK;
+}
+
 extern "C" int cc_batch_add_rows(cc_batch *b, cc_slice dst, cc_slice src, uint64_t src_stride, uint64_t rows,
                                  uint64_t width) {
     if (!b) return fail(CC_DISPATCH, "add_rows: null batch");

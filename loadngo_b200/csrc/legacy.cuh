@@ -37,6 +37,10 @@ void launch_topk_softmax(const float *logits, uint32_t *ids, float *weights, uin
 void launch_gemv_mxfp4_selected(const uint8_t *elements, const uint8_t *scales, const uint32_t *ids, const float *x,
                                 float *y, uint32_t rows, uint32_t cols, uint32_t k, uint32_t x_stride, uint32_t matrices,
                                 cudaStream_t stream);
+void launch_mxfp4(const uint8_t *elements, const uint8_t *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
+                  uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream);
+void launch_clamped_swiglu(const float *gate, const float *up, const float *gate_bias, const float *up_bias, float *out,
+                           uint32_t rows, uint32_t width, float limit, float alpha, cudaStream_t stream);
 void launch_clamped_swiglu_selected(const float *gate, const float *up, const float *gate_bias, const float *up_bias,
                                     const uint32_t *ids, float *out, uint32_t rows, uint32_t width, uint32_t experts,
                                     float limit, float alpha, cudaStream_t stream);

@@ -128,6 +128,85 @@ __global__ void __launch_bounds__(kMoeWarps * 32) gemv_mxfp4_selected_kernel(
     if (lane == 0) y[static_cast<size_t>(j) * rows + row] = acc;
 }
 
+// y[p] = W x[p] for n positions with one rows x cols MXFP4 matrix: `gemv_mxfp4`, `gemm_mxfp4` and
+// `gemm_mxfp4_tiled` (kernels.metal:112-186, 279-352, 1150-1227; a prompt pass runs every chosen
+// expert on the rows gathered for it, gpu.rs:1229-1286).  A warp owns two rows of the matrix; per
+// chunk of 1024 columns a lane reads one block (16 bytes) of each, and the x rows of up to kPos
+// positions sit in shared memory, so a matrix row is read once per kPos positions.
+template <int kPos>
+__global__ void __launch_bounds__(kMoeWarps * 32) mxfp4_kernel(const uint8_t *__restrict__ elements,
+                                                               const uint8_t *__restrict__ scales,
+                                                               const float *__restrict__ x, float *__restrict__ y,
+                                                               uint32_t rows, uint32_t cols, uint32_t n, uint32_t x_stride,
+                                                               uint32_t y_stride) {
+    constexpr int kChunk = 1024;
+    __shared__ __align__(16) float xs[kPos][kChunk];
+    __shared__ float lut[16];
+    if (threadIdx.x < 16) {
+        const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+        lut[threadIdx.x] = (threadIdx.x & 8) ? -mag[threadIdx.x & 7] : mag[threadIdx.x & 7];
+    }
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row0 = (blockIdx.x * kMoeWarps + warp) * 2;
+    const uint32_t p0 = blockIdx.y * kPos;
+    const uint32_t np = min(static_cast<uint32_t>(kPos), n - p0);
+    const uint32_t blocks = cols / 32;
+    float acc[2][kPos];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int p = 0; p < kPos; ++p) acc[r][p] = 0.f;
+    for (uint32_t c0 = 0; c0 < cols; c0 += kChunk) {
+        const uint32_t width = min(static_cast<uint32_t>(kChunk), cols - c0);
+        __syncthreads();
+        for (uint32_t i = threadIdx.x * 4; i < kPos * kChunk; i += kMoeWarps * 32 * 4) {
+            const uint32_t p = i / kChunk, c = i % kChunk;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p < np && c < width) v = *reinterpret_cast<const float4 *>(x + static_cast<size_t>(p0 + p) * x_stride + c0 + c);
+            *reinterpret_cast<float4 *>(&xs[p][c]) = v;
+        }
+        __syncthreads();
+        const uint32_t c = lane * 32;
+        if (c >= width) continue;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t row = row0 + r;
+            if (row >= rows) break;
+            const size_t b = static_cast<size_t>(row) * blocks + (c0 + c) / 32;
+            const uint4 q = reinterpret_cast<const uint4 *>(elements)[b];
+            const float d = e8m0(scales[b]);
+#pragma unroll
+            for (int p = 0; p < kPos; ++p) {
+                const float4 *xv = reinterpret_cast<const float4 *>(&xs[p][c]);
+                const float block = dot_e2m1x8(q.x, lut, xv[0], xv[1]) + dot_e2m1x8(q.y, lut, xv[2], xv[3]) +
+                                    dot_e2m1x8(q.z, lut, xv[4], xv[5]) + dot_e2m1x8(q.w, lut, xv[6], xv[7]);
+                acc[r][p] += block * d;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int p = 0; p < kPos; ++p) {
+            const float v = warp_sum(acc[r][p]);
+            if (lane == 0 && row0 + r < rows && static_cast<uint32_t>(p) < np)
+                y[static_cast<size_t>(p0 + p) * y_stride + row0 + r] = v;
+        }
+}
+
+// out = (clamp(up + ub) + 1) * g * sigmoid(alpha g), g = min(gate + gb, limit), one bias row for
+// all rows (`clamped_swiglu`, kernels.metal:1702-1720).
+__global__ void clamped_swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                      const float *__restrict__ gate_bias, const float *__restrict__ up_bias,
+                                      float *__restrict__ out, uint32_t rows, uint32_t width, float limit, float alpha) {
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= rows * width) return;
+    const uint32_t i = gid % width;
+    const float g = fminf(gate[gid] + gate_bias[i], limit);
+    const float u = fminf(fmaxf(up[gid] + up_bias[i], -limit), limit);
+    out[gid] = (u + 1.0f) * g / (1.0f + expf(-alpha * g));
+}
+
 // out = (clamp(up + ub) + 1) * g * sigmoid(alpha g), g = min(gate + gb, limit), biases of expert
 // ids[j] (kernels.metal:1893-1912; model.rs:517-525).
 __global__ void clamped_swiglu_selected_kernel(const float *__restrict__ gate, const float *__restrict__ up,
@@ -170,6 +249,20 @@ void launch_gemv_mxfp4_selected(const uint8_t *elements, const uint8_t *scales, 
                                 cudaStream_t stream) {
     gemv_mxfp4_selected_kernel<<<dim3((rows + kMoeWarps - 1) / kMoeWarps, k), kMoeWarps * 32, 0, stream>>>(
         elements, scales, ids, x, y, rows, cols, x_stride, matrices);
+}
+void launch_mxfp4(const uint8_t *elements, const uint8_t *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
+                  uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream) {
+    const unsigned row_blocks = (rows + kMoeWarps * 2 - 1) / (kMoeWarps * 2);
+    if (n == 1)
+        mxfp4_kernel<1><<<dim3(row_blocks, 1), kMoeWarps * 32, 0, stream>>>(elements, scales, x, y, rows, cols, n, x_stride, y_stride);
+    else
+        mxfp4_kernel<8><<<dim3(row_blocks, (n + 7) / 8), kMoeWarps * 32, 0, stream>>>(elements, scales, x, y, rows, cols, n, x_stride,
+                                                                                   y_stride);
+}
+void launch_clamped_swiglu(const float *gate, const float *up, const float *gate_bias, const float *up_bias, float *out,
+                           uint32_t rows, uint32_t width, float limit, float alpha, cudaStream_t stream) {
+    const uint32_t n = rows * width;
+    clamped_swiglu_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gate, up, gate_bias, up_bias, out, rows, width, limit, alpha);
 }
 void launch_clamped_swiglu_selected(const float *gate, const float *up, const float *gate_bias, const float *up_bias,
                                     const uint32_t *ids, float *out, uint32_t rows, uint32_t width, uint32_t experts,

@@ -145,3 +145,93 @@ def test_tiny_fixture_decoded_whole_on_the_gpu():
         assert float(np.abs(logits - g["logits"][p]).max()) < 2e-3
     model.free()
     gpu.free()
+
+
+@pytest.mark.parametrize("rows,cols,n,kind", [(2880, 2880, 1, "gemv"), (37, 96, 1, "gemv"), (64, 128, 5, "gemm"),
+                                               (37, 96, 13, "gemm"), (128, 2880, 32, "tiled"), (2880, 64, 96, "tiled")])
+def test_mxfp4_products_match_the_float64_definition(gpu, rows, cols, n, kind):
+    """One matrix, n positions: the plain and the tiled entry against every element's value times x
+    in float64 (the reference's bound for its MXFP4 products, relative 1e-5)."""
+    rng = np.random.default_rng(rows + cols + n)
+    elements, scales, w = mxfp4(rng, 1, rows, cols)
+    x = values(11, n * cols)
+    bufs = [gpu.upload(elements), gpu.upload(scales), gpu.upload(x), gpu.buffer(n * rows * 4)]
+    batch = gpu.batch(bufs)
+    e, s_, xs, ys = Slice(0, 0, elements.size), Slice(1, 0, scales.size), Slice(2, 0, x.size * 4), Slice(3, 0, n * rows * 4)
+    if kind == "gemv":
+        batch.gemv_mxfp4(e, s_, xs, ys, rows, cols)
+    elif kind == "gemm":
+        batch.gemm_mxfp4(e, s_, xs, ys, rows, cols, n, (cols, rows))
+    else:
+        batch.gemm_mxfp4_tiled(e, s_, xs, ys, rows, cols, n, (cols, rows))
+    done = batch.run()
+    assert not isinstance(done.gpu_time, Exception), done.gpu_time
+    got = bufs[3].as_f32()[: n * rows].reshape(n, rows)
+    want = x.reshape(n, cols).astype(np.float64) @ w[0].T
+    assert np.abs(got - want).max() / np.abs(want).max() < 1e-5
+    for b in bufs:
+        b.free()
+
+
+def test_clamped_swiglu_matches_its_definition(gpu):
+    rows, width = 7, 96
+    gate, up = values(41, rows * width) * np.float32(9.0), values(42, rows * width) * np.float32(9.0)
+    gb, ub = values(43, width), values(44, width)
+    bufs = [gpu.upload(gate), gpu.upload(up), gpu.upload(gb), gpu.upload(ub), gpu.buffer(rows * width * 4)]
+    batch = gpu.batch(bufs)
+    f = lambda b, n: Slice(b, 0, n * 4)
+    batch.clamped_swiglu((f(0, rows * width), f(1, rows * width)), (f(2, width), f(3, width)), f(4, rows * width), rows, width,
+                         (7.0, 1.702))
+    assert not isinstance(batch.run().gpu_time, Exception)
+    g = np.minimum(gate.reshape(rows, width).astype(np.float64) + gb, 7.0)
+    u = np.clip(up.reshape(rows, width).astype(np.float64) + ub, -7.0, 7.0)
+    want = (u + 1.0) * g / (1.0 + np.exp(-1.702 * g))
+    assert np.abs(bufs[4].as_f32()[: rows * width].reshape(rows, width) - want).max() < 1e-5
+    for b in bufs:
+        b.free()
+
+
+def _tiny_model(chunk):
+    g = np.load(BLOCK_GOLDEN)
+    meta = json.loads(str(g["meta"]))
+    cfg = Config(layers=meta["layers"], hidden=meta["hidden"], heads=meta["heads"], kv_heads=meta["kv_heads"],
+                 head_dim=meta["dim"], window=meta["window"], eps=meta["eps"], experts=meta["experts"],
+                 experts_used=meta["experts_used"], expert_hidden=meta["expert_hidden"], vocab=meta["vocab"],
+                 theta=meta["theta"], factor=meta["factor"], original_context=float(meta["original_context"]))
+    tensors = {"output.weight": g["output_q8_0"], "output_norm.weight": g["output_norm"]}
+    for l in range(cfg.layers):
+        for name in ("attn_q", "attn_k", "attn_v", "attn_output"):
+            tensors[f"blk.{l}.{name}.weight"] = g[f"l{l}_{name}_q8_0"]
+            tensors[f"blk.{l}.{name}.bias"] = g[f"l{l}_{name}_bias"]
+        tensors[f"blk.{l}.attn_norm.weight"] = g[f"l{l}_attn_norm"]
+        tensors[f"blk.{l}.post_attention_norm.weight"] = g[f"l{l}_ffn_norm"]
+        tensors[f"blk.{l}.attn_sinks.weight"] = g[f"l{l}_sinks"]
+        tensors[f"blk.{l}.ffn_gate_inp.weight"] = g[f"l{l}_router"]
+        tensors[f"blk.{l}.ffn_gate_inp.bias"] = g[f"l{l}_router_bias"]
+        for name in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
+            tensors[f"blk.{l}.{name}.weight"] = g[f"l{l}_{name}_mxfp4"]
+            tensors[f"blk.{l}.{name}.bias"] = g[f"l{l}_{name}_bias"]
+    gpu = compute.Gpu(0)
+    return gpu, GpuModel(gpu, cfg, tensors, capacity=meta["positions"], chunk=chunk), g, meta
+
+
+@pytest.mark.parametrize("chunks", [[8] * 5, [33, 7], [16, 1, 1, 22]])
+def test_tiny_fixture_prompt_passes_on_the_gpu(chunks):
+    """The fixture fed as gpt-oss/tests/gpu_oracle.rs:76-145 feeds it: in chunks of 8, as 33 + 7
+    (the tiled kernels on 64 padded rows, then the plain ones), and a prompt pass followed by single
+    tokens and another pass.  Per layer the attention half is one submission, routing and
+    gathering happen on the CPU, the experts are a second submission; every position's logits
+    match the fixture's within 2e-3."""
+    gpu, model, g, meta = _tiny_model(max(chunks))
+    start, worst = 0, 0.0
+    for n in chunks:
+        if n == 1:
+            logits = model.step(g["embedded"][start])[None]
+        else:
+            logits = model.prompt_pass(g["embedded"][start:start + n], all_logits=True)
+        worst = max(worst, float(np.abs(logits - g["logits"][start:start + n]).max()))
+        start += n
+    print(f"\ntiny fixture, passes of {chunks}: worst logit error {worst:.3e}")
+    assert worst < 2e-3
+    model.free()
+    gpu.free()
