@@ -429,6 +429,80 @@ void cc_batch_drop(cc_batch *batch);
 /* Dispatches recorded so far. */
 uint32_t cc_batch_dispatches(const cc_batch *batch);
 
+/* ---- G. GGUF headers (host code, no device needed) --------------------------------------------
+ *
+ * What a gpt-oss model is loaded from: `Gguf` of loadngo's `weights` crate
+ * (weights/src/gguf.rs).  These functions return a cc_gguf_status, not a cc_status; the
+ * message is in cc_last_error() as usual. */
+
+/* `GgufError` (weights/src/gguf.rs:147-163). */
+typedef enum cc_gguf_status {
+    CC_GGUF_OK = 0,
+    CC_GGUF_MAGIC = 1,      /* not a GGUF file */
+    CC_GGUF_VERSION = 2,    /* only versions 2 and 3 are read */
+    CC_GGUF_TRUNCATED = 3,  /* the header needs more of the file than the prefix holds */
+    CC_GGUF_VALUE_TYPE = 4, /* unknown metadata value type */
+    CC_GGUF_UTF8 = 5,       /* a string is not UTF-8 */
+    CC_GGUF_INVALID = 6,    /* a count, offset, size or repeat that cannot be right */
+    CC_GGUF_READ = 7        /* the file could not be opened or read */
+} cc_gguf_status;
+
+/* Metadata value types, by their GGUF numbers (`Value`, gguf.rs:30-46). */
+enum {
+    CC_GGUF_U8 = 0, CC_GGUF_I8 = 1, CC_GGUF_U16 = 2, CC_GGUF_I16 = 3, CC_GGUF_U32 = 4, CC_GGUF_I32 = 5,
+    CC_GGUF_F32 = 6, CC_GGUF_BOOL = 7, CC_GGUF_STRING = 8, CC_GGUF_ARRAY = 9, CC_GGUF_U64 = 10,
+    CC_GGUF_I64 = 11, CC_GGUF_F64 = 12
+};
+
+/* Element types this reader sizes (`GgmlType`, gguf.rs:88-125), by their ggml numbers. */
+enum { CC_GGML_F32 = 0, CC_GGML_F16 = 1, CC_GGML_Q8_0 = 8, CC_GGML_BF16 = 30, CC_GGML_MXFP4 = 39 };
+
+typedef struct cc_gguf cc_gguf;
+
+/* `Tensor` (gguf.rs:127-139).  `name` lives as long as the cc_gguf; dims beyond n_dims are 1;
+ * `offset` is absolute in the file; `len` is UINT64_MAX for an element type that is not sized. */
+typedef struct cc_gguf_tensor {
+    const char *name;
+    uint32_t n_dims;
+    uint64_t dims[8]; /* the first varies fastest: a matrix of `rows` rows of `cols` is [cols, rows] */
+    uint32_t ggml_type;
+    uint64_t offset;
+    uint64_t len;
+} cc_gguf_tensor;
+
+/* `Gguf::parse` (gguf.rs:258-351): the header from the file's first bytes. */
+int cc_gguf_parse(const uint8_t *prefix, uint64_t prefix_len, uint64_t file_len, cc_gguf **out);
+/* `gguf::open` + `Gguf::read` (gguf.rs:354-408): reads the first `first_read` bytes (16 MiB when
+ * 0), doubling while the header is longer, and keeps the file open for cc_gguf_read. */
+int cc_gguf_open(const char *path, uint64_t first_read, cc_gguf **out);
+void cc_gguf_free(cc_gguf *gguf);
+uint32_t cc_gguf_version(const cc_gguf *gguf);
+uint64_t cc_gguf_alignment(const cc_gguf *gguf);
+uint64_t cc_gguf_data_offset(const cc_gguf *gguf);
+uint64_t cc_gguf_tensor_count(const cc_gguf *gguf);
+int cc_gguf_tensor_at(const cc_gguf *gguf, uint64_t index, cc_gguf_tensor *out);
+/* `Gguf::tensor` (gguf.rs:384-386): the tensor's index, or -1. */
+int64_t cc_gguf_find_tensor(const cc_gguf *gguf, const char *name);
+uint64_t cc_gguf_metadata_count(const cc_gguf *gguf);
+/* The index-th key in sorted order (the reference keeps a BTreeMap), or NULL. */
+const char *cc_gguf_metadata_key(const cc_gguf *gguf, uint64_t index);
+/* The value's type, or -1 when the key is absent; for arrays the element type and length. */
+int cc_gguf_value_type(const cc_gguf *gguf, const char *key);
+int cc_gguf_array_type(const cc_gguf *gguf, const char *key);
+uint64_t cc_gguf_array_len(const cc_gguf *gguf, const char *key);
+/* Getters return 1 and fill `out` when the key exists and converts, else 0.  index < 0 reads
+ * the value itself, index >= 0 an element of an array value.  cc_gguf_get_u64 is
+ * `Value::as_u64` (any integer type, not negative), cc_gguf_get_f64 `Value::as_f64` (f32 or
+ * f64 only), cc_gguf_get_str `Value::as_str` (not NUL-terminated: use `len`). */
+int cc_gguf_get_u64(const cc_gguf *gguf, const char *key, int64_t index, uint64_t *out);
+int cc_gguf_get_i64(const cc_gguf *gguf, const char *key, int64_t index, int64_t *out);
+int cc_gguf_get_f64(const cc_gguf *gguf, const char *key, int64_t index, double *out);
+int cc_gguf_get_bool(const cc_gguf *gguf, const char *key, int64_t index, int *out);
+int cc_gguf_get_str(const cc_gguf *gguf, const char *key, int64_t index, const char **text, uint64_t *len);
+/* Bytes [offset, offset + len) of a file opened with cc_gguf_open (the reference reads every
+ * tensor's range in one batch through its proactor, gpt-oss/src/model.rs:291-309). */
+int cc_gguf_read(const cc_gguf *gguf, uint64_t offset, uint64_t len, void *dst);
+
 #ifdef __cplusplus
 }
 #endif

@@ -120,6 +120,12 @@ class PagedCache(Structure):
                 ("ring_pages", c_uint32), ("kv_heads", c_uint32)]
 
 
+class GgufTensor(Structure):
+    """`cc_gguf_tensor`: `Tensor` of weights/src/gguf.rs:127-139."""
+    _fields_ = [("name", c_char_p), ("n_dims", c_uint32), ("dims", c_uint64 * 8), ("ggml_type", c_uint32),
+                ("offset", c_uint64), ("len", c_uint64)]
+
+
 COMPLETION_FN = ctypes.CFUNCTYPE(None, c_void_p, c_int, c_char_p, c_double)
 
 # name -> (restype, argtypes): every symbol include/cuda_compute.h declares.
@@ -212,6 +218,26 @@ SYMBOLS = {
     "cc_batch_replay_wait": (c_int, [c_void_p, POINTER(c_double)]),
     "cc_batch_drop": (None, [c_void_p]),
     "cc_batch_dispatches": (c_uint32, [c_void_p]),
+    "cc_gguf_parse": (c_int, [c_void_p, c_uint64, c_uint64, POINTER(c_void_p)]),
+    "cc_gguf_open": (c_int, [c_char_p, c_uint64, POINTER(c_void_p)]),
+    "cc_gguf_free": (None, [c_void_p]),
+    "cc_gguf_version": (c_uint32, [c_void_p]),
+    "cc_gguf_alignment": (c_uint64, [c_void_p]),
+    "cc_gguf_data_offset": (c_uint64, [c_void_p]),
+    "cc_gguf_tensor_count": (c_uint64, [c_void_p]),
+    "cc_gguf_tensor_at": (c_int, [c_void_p, c_uint64, POINTER(GgufTensor)]),
+    "cc_gguf_find_tensor": (ctypes.c_int64, [c_void_p, c_char_p]),
+    "cc_gguf_metadata_count": (c_uint64, [c_void_p]),
+    "cc_gguf_metadata_key": (c_char_p, [c_void_p, c_uint64]),
+    "cc_gguf_value_type": (c_int, [c_void_p, c_char_p]),
+    "cc_gguf_array_type": (c_int, [c_void_p, c_char_p]),
+    "cc_gguf_array_len": (c_uint64, [c_void_p, c_char_p]),
+    "cc_gguf_get_u64": (c_int, [c_void_p, c_char_p, ctypes.c_int64, POINTER(c_uint64)]),
+    "cc_gguf_get_i64": (c_int, [c_void_p, c_char_p, ctypes.c_int64, POINTER(ctypes.c_int64)]),
+    "cc_gguf_get_f64": (c_int, [c_void_p, c_char_p, ctypes.c_int64, POINTER(c_double)]),
+    "cc_gguf_get_bool": (c_int, [c_void_p, c_char_p, ctypes.c_int64, POINTER(c_int)]),
+    "cc_gguf_get_str": (c_int, [c_void_p, c_char_p, ctypes.c_int64, POINTER(c_void_p), POINTER(c_uint64)]),
+    "cc_gguf_read": (c_int, [c_void_p, c_uint64, c_uint64, c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,447 @@
+// GGUF header reader (host code only): what loadngo's `weights` crate does in
+// weights/src/gguf.rs:255-391 before a gpt-oss model's tensors are copied to the GPU.
+//
+// A file is the magic "GGUF", a u32 version (2 or 3), a u64 tensor count, a u64 metadata count,
+// the metadata entries (key string, u32 value type, value), the tensor descriptions (name, u32
+// dimension count, u64 dimensions with the first varying fastest, u32 ggml type, u64 offset from
+// the start of the data) and, after padding to `general.alignment` (32 when absent), the data.
+// Strings are a u64 byte length followed by UTF-8.  Everything is little-endian.
+#include <cerrno>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include "../../include/cuda_compute.h"
+#include "kernels.cuh"
+
+namespace {
+
+struct Value {
+    uint32_t type = 0;          // GGUF value type, 0..12
+    uint64_t bits = 0;          // integers (sign-extended), bool, or the IEEE bits of f32 / f64
+    std::string text;           // type 8
+    uint32_t element_type = 0;  // type 9
+    std::vector<Value> items;   // type 9
+};
+
+struct Tensor {
+    std::string name;
+    std::vector<uint64_t> dims;
+    uint32_t ggml_type = 0;
+    uint64_t offset = 0;             // absolute
+    uint64_t len = UINT64_MAX;       // UINT64_MAX: a type this reader does not size
+};
+
+}  // namespace
+
+struct cc_gguf {
+    uint32_t version = 0;
+    uint64_t alignment = 32;
+    uint64_t data_offset = 0;
+    std::map<std::string, Value> metadata;
+    std::vector<const std::string *> keys;   // in sorted order, for cc_gguf_metadata_key
+    std::vector<Tensor> tensors;
+    int fd = -1;
+};
+
+namespace {
+
+int fail(int code, const std::string &text) {
+    cc::set_error(CC_DISPATCH, text.c_str());   // leaves the message for cc_last_error()
+    return code;
+}
+
+// Rust's String::from_utf8: no overlong forms, no surrogates, nothing above U+10FFFF.
+bool valid_utf8(const uint8_t *s, size_t n) {
+    size_t i = 0;
+    while (i < n) {
+        const uint8_t b = s[i];
+        if (b < 0x80) { ++i; continue; }
+        size_t extra;
+        uint32_t cp;
+        if (b >= 0xc2 && b <= 0xdf) { extra = 1; cp = b & 0x1f; }
+        else if (b >= 0xe0 && b <= 0xef) { extra = 2; cp = b & 0x0f; }
+        else if (b >= 0xf0 && b <= 0xf4) { extra = 3; cp = b & 0x07; }
+        else return false;
+        if (i + extra >= n) return false;
+        for (size_t k = 1; k <= extra; ++k) {
+            if ((s[i + k] & 0xc0) != 0x80) return false;
+            cp = (cp << 6) | (s[i + k] & 0x3f);
+        }
+        if (extra == 2 && (cp < 0x800 || (cp >= 0xd800 && cp <= 0xdfff))) return false;
+        if (extra == 3 && (cp < 0x10000 || cp > 0x10ffff)) return false;
+        i += extra + 1;
+    }
+    return true;
+}
+
+// Element types with known sizes (gguf.rs:103-124): (elements per block, bytes per block).
+bool block_of(uint32_t ggml_type, uint64_t *elements, uint64_t *bytes) {
+    switch (ggml_type) {
+        case 0: *elements = 1; *bytes = 4; return true;     // F32
+        case 1: *elements = 1; *bytes = 2; return true;     // F16
+        case 8: *elements = 32; *bytes = 34; return true;   // Q8_0
+        case 30: *elements = 1; *bytes = 2; return true;    // BF16
+        case 39: *elements = 32; *bytes = 17; return true;  // MXFP4
+        default: return false;
+    }
+}
+
+struct Cursor {
+    const uint8_t *bytes;
+    uint64_t size;
+    uint64_t at = 0;
+    int error = CC_GGUF_OK;
+    std::string message;
+
+    bool take(uint64_t n, const uint8_t **out) {
+        if (n > size - at) {
+            error = CC_GGUF_TRUNCATED;
+            message = "the header continues past the " + std::to_string(size) + " bytes read";
+            return false;
+        }
+        *out = bytes + at;
+        at += n;
+        return true;
+    }
+    template <typename T>
+    bool scalar(T *out) {
+        const uint8_t *p;
+        if (!take(sizeof(T), &p)) return false;
+        std::memcpy(out, p, sizeof(T));   // the hosts this builds for are little-endian
+        return true;
+    }
+    // A length past the bytes at hand is a longer header or a corrupt one: more bytes decide.
+    bool length(uint64_t *out) {
+        if (!scalar(out)) return false;
+        if (*out > size) {
+            error = CC_GGUF_TRUNCATED;
+            message = "the header continues past the " + std::to_string(size) + " bytes read";
+            return false;
+        }
+        return true;
+    }
+    bool string(std::string *out) {
+        uint64_t n;
+        const uint8_t *p;
+        if (!length(&n) || !take(n, &p)) return false;
+        if (!valid_utf8(p, n)) {
+            error = CC_GGUF_UTF8;
+            message = "a GGUF string is not UTF-8";
+            return false;
+        }
+        out->assign(reinterpret_cast<const char *>(p), n);
+        return true;
+    }
+    bool invalid(const std::string &text) {
+        error = CC_GGUF_INVALID;
+        message = text;
+        return false;
+    }
+    bool value(uint32_t type, int depth, Value *out) {
+        out->type = type;
+        switch (type) {
+            case 0: { uint8_t v; if (!scalar(&v)) return false; out->bits = v; return true; }
+            case 1: { int8_t v; if (!scalar(&v)) return false; out->bits = static_cast<uint64_t>(static_cast<int64_t>(v)); return true; }
+            case 2: { uint16_t v; if (!scalar(&v)) return false; out->bits = v; return true; }
+            case 3: { int16_t v; if (!scalar(&v)) return false; out->bits = static_cast<uint64_t>(static_cast<int64_t>(v)); return true; }
+            case 4: { uint32_t v; if (!scalar(&v)) return false; out->bits = v; return true; }
+            case 5: { int32_t v; if (!scalar(&v)) return false; out->bits = static_cast<uint64_t>(static_cast<int64_t>(v)); return true; }
+            case 6: { uint32_t v; if (!scalar(&v)) return false; out->bits = v; return true; }
+            case 7: {
+                uint8_t v;
+                if (!scalar(&v)) return false;
+                if (v > 1) return invalid("bool byte " + std::to_string(v));
+                out->bits = v;
+                return true;
+            }
+            case 8: return string(&out->text);
+            case 9: {
+                if (depth > 0) return invalid("nested metadata arrays");
+                uint64_t n;
+                if (!scalar(&out->element_type) || !length(&n)) return false;
+                out->items.reserve(n);
+                for (uint64_t i = 0; i < n; ++i) {
+                    out->items.emplace_back();
+                    if (!value(out->element_type, depth + 1, &out->items.back())) return false;
+                }
+                return true;
+            }
+            case 10: case 11: case 12: return scalar(&out->bits);
+            default:
+                error = CC_GGUF_VALUE_TYPE;
+                message = "metadata value type " + std::to_string(type) + " is unknown";
+                return false;
+        }
+    }
+};
+
+// Value::as_u64 (gguf.rs:50-62): any integer type whose value is not negative.
+bool as_u64(const Value &v, uint64_t *out) {
+    switch (v.type) {
+        case 0: case 2: case 4: case 10: *out = v.bits; return true;
+        case 1: case 3: case 5: case 11:
+            if (static_cast<int64_t>(v.bits) < 0) return false;
+            *out = v.bits;
+            return true;
+        default: return false;
+    }
+}
+
+int parse(const uint8_t *prefix, uint64_t prefix_len, uint64_t file_len, cc_gguf *g) {
+    Cursor at{prefix, prefix_len};
+    const uint8_t *magic;
+    if (!at.take(4, &magic)) return fail(at.error, at.message);
+    if (std::memcmp(magic, "GGUF", 4) != 0) {
+        char text[64];
+        std::snprintf(text, sizeof text, "not a GGUF file (magic [%02x, %02x, %02x, %02x])", magic[0], magic[1], magic[2],
+                      magic[3]);
+        return fail(CC_GGUF_MAGIC, text);
+    }
+    if (!at.scalar(&g->version)) return fail(at.error, at.message);
+    if (g->version < 2 || g->version > 3)
+        return fail(CC_GGUF_VERSION, "GGUF version " + std::to_string(g->version) + " is not supported (2 and 3 are)");
+    uint64_t tensor_count, metadata_count;
+    if (!at.length(&tensor_count) || !at.length(&metadata_count)) return fail(at.error, at.message);
+    for (uint64_t i = 0; i < metadata_count; ++i) {
+        std::string key;
+        uint32_t type;
+        Value value;
+        if (!at.string(&key) || !at.scalar(&type) || !at.value(type, 0, &value)) return fail(at.error, at.message);
+        if (!g->metadata.emplace(key, std::move(value)).second)
+            return fail(CC_GGUF_INVALID, "metadata key \"" + key + "\" repeats");
+    }
+    const auto alignment = g->metadata.find("general.alignment");
+    if (alignment != g->metadata.end()) {
+        uint64_t a;
+        if (!as_u64(alignment->second, &a) || a == 0 || (a & (a - 1)) != 0) return fail(CC_GGUF_INVALID, "general.alignment");
+        g->alignment = a;
+    }
+    struct Described { std::string name; std::vector<uint64_t> dims; uint32_t type; uint64_t relative; };
+    std::vector<Described> described;
+    described.reserve(tensor_count);
+    for (uint64_t i = 0; i < tensor_count; ++i) {
+        Described d;
+        uint32_t n_dims;
+        if (!at.string(&d.name) || !at.scalar(&n_dims)) return fail(at.error, at.message);
+        if (n_dims == 0 || n_dims > 8) return fail(CC_GGUF_INVALID, d.name + ": " + std::to_string(n_dims) + " dimensions");
+        d.dims.resize(n_dims);
+        for (auto &dim : d.dims)
+            if (!at.scalar(&dim)) return fail(at.error, at.message);
+        if (!at.scalar(&d.type) || !at.scalar(&d.relative)) return fail(at.error, at.message);
+        described.push_back(std::move(d));
+    }
+    const uint64_t a = g->alignment;
+    g->data_offset = (at.at + a - 1) / a * a;
+    if (file_len < g->data_offset) return fail(CC_GGUF_INVALID, "the file ends inside its header");
+    const uint64_t data_len = file_len - g->data_offset;
+    for (auto &d : described) {
+        if (d.relative % a != 0) return fail(CC_GGUF_INVALID, d.name + ": unaligned offset");
+        uint64_t numel = 1;
+        for (uint64_t dim : d.dims)
+            if (__builtin_mul_overflow(numel, dim, &numel)) return fail(CC_GGUF_INVALID, d.name + ": size overflows");
+        Tensor t;
+        uint64_t elements, bytes;
+        if (block_of(d.type, &elements, &bytes)) {
+            if (d.dims[0] % elements != 0)
+                return fail(CC_GGUF_INVALID, d.name + ": rows of " + std::to_string(d.dims[0]) + " are not whole blocks of " +
+                                                 std::to_string(elements));
+            uint64_t len, end;
+            if (__builtin_mul_overflow(numel / elements, bytes, &len)) return fail(CC_GGUF_INVALID, d.name + ": size overflows");
+            if (__builtin_add_overflow(d.relative, len, &end) || end > data_len)
+                return fail(CC_GGUF_INVALID, d.name + ": past the end of the file");
+            t.len = len;
+        }
+        t.name = std::move(d.name);
+        t.dims = std::move(d.dims);
+        t.ggml_type = d.type;
+        t.offset = g->data_offset + d.relative;
+        g->tensors.push_back(std::move(t));
+    }
+    for (const auto &entry : g->metadata) g->keys.push_back(&entry.first);
+    return CC_GGUF_OK;
+}
+
+const Value *find(const cc_gguf *g, const char *key, int64_t index) {
+    if (!g || !key) return nullptr;
+    const auto it = g->metadata.find(key);
+    if (it == g->metadata.end()) return nullptr;
+    if (index < 0) return &it->second;
+    if (it->second.type != 9 || static_cast<uint64_t>(index) >= it->second.items.size()) return nullptr;
+    return &it->second.items[index];
+}
+
+}  // namespace
+
+extern "C" int cc_gguf_parse(const uint8_t *prefix, uint64_t prefix_len, uint64_t file_len, cc_gguf **out) {
+    if (!prefix || !out) return fail(CC_GGUF_INVALID, "cc_gguf_parse: null argument");
+    auto *g = new cc_gguf;
+    const int code = parse(prefix, prefix_len, file_len, g);
+    if (code != CC_GGUF_OK) {
+        delete g;
+        return code;
+    }
+    *out = g;
+    return CC_GGUF_OK;
+}
+
+// Reads the header in pieces of `first_read` bytes (16 MiB when 0), doubled until it fits
+// (gguf.rs:358-382), and keeps the file open for cc_gguf_read.
+extern "C" int cc_gguf_open(const char *path, uint64_t first_read, cc_gguf **out) {
+    if (!path || !out) return fail(CC_GGUF_INVALID, "cc_gguf_open: null argument");
+    const int fd = ::open(path, O_RDONLY | O_CLOEXEC);
+    struct stat st;
+    if (fd < 0 || ::fstat(fd, &st) != 0) {
+        if (fd >= 0) ::close(fd);
+        return fail(CC_GGUF_READ, std::string("cannot open ") + path + ": " + std::strerror(errno));
+    }
+    const uint64_t file_len = static_cast<uint64_t>(st.st_size);
+    uint64_t want = first_read ? first_read : 16ull * 1024 * 1024;
+    std::vector<uint8_t> prefix;
+    for (;;) {
+        const uint64_t take = want < file_len ? want : file_len;
+        prefix.resize(take);
+        uint64_t got = 0;
+        while (got < take) {
+            const ssize_t n = ::pread(fd, prefix.data() + got, take - got, static_cast<off_t>(got));
+            if (n <= 0) {
+                ::close(fd);
+                return fail(CC_GGUF_READ, std::string("cannot read ") + path + " (GGUF header)");
+            }
+            got += static_cast<uint64_t>(n);
+        }
+        auto *g = new cc_gguf;
+        const int code = parse(prefix.data(), take, file_len, g);
+        if (code == CC_GGUF_OK) {
+            g->fd = fd;
+            *out = g;
+            return CC_GGUF_OK;
+        }
+        delete g;
+        if (code == CC_GGUF_TRUNCATED && take < file_len) {
+            want *= 2;
+            continue;
+        }
+        ::close(fd);
+        return code;
+    }
+}
+
+extern "C" void cc_gguf_free(cc_gguf *g) {
+    if (!g) return;
+    if (g->fd >= 0) ::close(g->fd);
+    delete g;
+}
+
+extern "C" uint32_t cc_gguf_version(const cc_gguf *g) { return g ? g->version : 0; }
+extern "C" uint64_t cc_gguf_alignment(const cc_gguf *g) { return g ? g->alignment : 0; }
+extern "C" uint64_t cc_gguf_data_offset(const cc_gguf *g) { return g ? g->data_offset : 0; }
+extern "C" uint64_t cc_gguf_tensor_count(const cc_gguf *g) { return g ? g->tensors.size() : 0; }
+extern "C" uint64_t cc_gguf_metadata_count(const cc_gguf *g) { return g ? g->keys.size() : 0; }
+
+extern "C" int cc_gguf_tensor_at(const cc_gguf *g, uint64_t index, cc_gguf_tensor *out) {
+    if (!g || !out || index >= g->tensors.size()) return fail(CC_GGUF_INVALID, "cc_gguf_tensor_at: no such tensor");
+    const Tensor &t = g->tensors[index];
+    out->name = t.name.c_str();
+    out->n_dims = static_cast<uint32_t>(t.dims.size());
+    for (size_t i = 0; i < 8; ++i) out->dims[i] = i < t.dims.size() ? t.dims[i] : 1;
+    out->ggml_type = t.ggml_type;
+    out->offset = t.offset;
+    out->len = t.len;
+    return CC_GGUF_OK;
+}
+
+extern "C" int64_t cc_gguf_find_tensor(const cc_gguf *g, const char *name) {
+    if (!g || !name) return -1;
+    for (size_t i = 0; i < g->tensors.size(); ++i)
+        if (g->tensors[i].name == name) return static_cast<int64_t>(i);
+    return -1;
+}
+
+extern "C" const char *cc_gguf_metadata_key(const cc_gguf *g, uint64_t index) {
+    return g && index < g->keys.size() ? g->keys[index]->c_str() : nullptr;
+}
+
+extern "C" int cc_gguf_value_type(const cc_gguf *g, const char *key) {
+    const Value *v = find(g, key, -1);
+    return v ? static_cast<int>(v->type) : -1;
+}
+
+extern "C" int cc_gguf_array_type(const cc_gguf *g, const char *key) {
+    const Value *v = find(g, key, -1);
+    return v && v->type == 9 ? static_cast<int>(v->element_type) : -1;
+}
+
+extern "C" uint64_t cc_gguf_array_len(const cc_gguf *g, const char *key) {
+    const Value *v = find(g, key, -1);
+    return v && v->type == 9 ? v->items.size() : 0;
+}
+
+extern "C" int cc_gguf_get_u64(const cc_gguf *g, const char *key, int64_t index, uint64_t *out) {
+    const Value *v = find(g, key, index);
+    return v && out && as_u64(*v, out) ? 1 : 0;
+}
+
+extern "C" int cc_gguf_get_i64(const cc_gguf *g, const char *key, int64_t index, int64_t *out) {
+    const Value *v = find(g, key, index);
+    if (!v || !out) return 0;
+    switch (v->type) {
+        case 0: case 1: case 2: case 3: case 4: case 5: case 11: *out = static_cast<int64_t>(v->bits); return 1;
+        case 10:
+            if (v->bits > static_cast<uint64_t>(INT64_MAX)) return 0;
+            *out = static_cast<int64_t>(v->bits);
+            return 1;
+        default: return 0;
+    }
+}
+
+// Value::as_f64 (gguf.rs:65-71): f32 or f64 only.
+extern "C" int cc_gguf_get_f64(const cc_gguf *g, const char *key, int64_t index, double *out) {
+    const Value *v = find(g, key, index);
+    if (!v || !out) return 0;
+    if (v->type == 6) {
+        const uint32_t bits = static_cast<uint32_t>(v->bits);
+        float f;
+        std::memcpy(&f, &bits, 4);
+        *out = static_cast<double>(f);
+        return 1;
+    }
+    if (v->type == 12) {
+        std::memcpy(out, &v->bits, 8);
+        return 1;
+    }
+    return 0;
+}
+
+extern "C" int cc_gguf_get_bool(const cc_gguf *g, const char *key, int64_t index, int *out) {
+    const Value *v = find(g, key, index);
+    if (!v || !out || v->type != 7) return 0;
+    *out = static_cast<int>(v->bits);
+    return 1;
+}
+
+extern "C" int cc_gguf_get_str(const cc_gguf *g, const char *key, int64_t index, const char **text, uint64_t *len) {
+    const Value *v = find(g, key, index);
+    if (!v || !text || !len || v->type != 8) return 0;
+    *text = v->text.data();
+    *len = v->text.size();
+    return 1;
+}
+
+extern "C" int cc_gguf_read(const cc_gguf *g, uint64_t offset, uint64_t len, void *dst) {
+    if (!g || g->fd < 0 || (!dst && len)) return fail(CC_GGUF_READ, "cc_gguf_read: the header was not opened from a file");
+    uint64_t got = 0;
+    while (got < len) {
+        const ssize_t n = ::pread(g->fd, static_cast<uint8_t *>(dst) + got, len - got, static_cast<off_t>(offset + got));
+        if (n <= 0) return fail(CC_GGUF_READ, "the file ends before byte " + std::to_string(offset + len));
+        got += static_cast<uint64_t>(n);
+    }
+    return CC_GGUF_OK;
+}

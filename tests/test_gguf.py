@@ -1,0 +1,163 @@
+"""The GGUF reader (host code of libcuda_compute.so) against files written by the tests' own
+writer, in the cases the reference's reader is tested on (weights/src/gguf.rs:493-571), and
+against the reference's tiny model file where the reference checkout is present."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+from loadngo_b200 import gguf
+
+import gguf_writer as w
+
+TINY = "/root/reference/gpt-oss/tests/fixtures/tiny/model.gguf"
+
+
+def sample() -> bytes:
+    return w.file(
+        [("general.architecture", w.STRING, "gpt-oss"),
+         ("gpt-oss.block_count", w.U32, 24),
+         ("gpt-oss.rope.freq_base", w.F32, 150000.0),
+         ("tokenizer.ggml.merges", w.ARRAY, (w.STRING, ["a b", "é"]))],
+        [("norm", [3], gguf.F32, np.array([1.0, 2.0, 3.0], np.float32)),
+         ("q", [32, 2], gguf.Q8_0, bytes(range(68))),
+         ("odd", [5], 2, bytes([9] * 18))])
+
+
+def test_metadata_and_tensors_parse_with_absolute_aligned_offsets():
+    raw = sample()
+    g = gguf.Gguf.parse(raw, len(raw))
+    assert g.version == 3 and g.alignment == 32
+    assert g.get("general.architecture") == "gpt-oss"
+    assert g.get("gpt-oss.block_count") == 24
+    assert g.get("gpt-oss.rope.freq_base") == 150000.0
+    assert g.get("tokenizer.ggml.merges") == ["a b", "é"]
+    assert g.get("absent") is None
+    assert g.keys() == sorted(["general.architecture", "gpt-oss.block_count", "gpt-oss.rope.freq_base",
+                               "tokenizer.ggml.merges"])
+    assert g.data_offset % 32 == 0
+    norm = g.tensor("norm")
+    assert (norm.ggml_type, norm.len, norm.dims) == (gguf.F32, 12, [3])
+    assert raw[norm.offset:norm.offset + 4] == struct.pack("<f", 1.0)
+    q = g.tensor("q")
+    assert (q.ggml_type, q.len, q.numel()) == (gguf.Q8_0, 68, 64)
+    assert q.offset - g.data_offset == 32
+    assert raw[q.offset + 67] == 67
+    assert g.tensor("odd").len is None, "Q4_0 is not sized here"
+    assert g.tensor("nothing") is None
+
+
+def test_a_short_prefix_asks_for_more_and_bad_files_are_refused():
+    raw = sample()
+    with pytest.raises(gguf.Truncated, match="40 bytes"):
+        gguf.Gguf.parse(raw[:40], len(raw))
+    with pytest.raises(gguf.Magic):
+        gguf.Gguf.parse(b"X" + raw[1:], len(raw))
+    with pytest.raises(gguf.Version, match="version 1"):
+        gguf.Gguf.parse(raw[:4] + struct.pack("<I", 1) + raw[8:], len(raw))
+    with pytest.raises(gguf.Invalid, match="past the end"):
+        gguf.Gguf.parse(raw, len(raw) - 70)          # the file is cut inside q, the last sized tensor
+    with pytest.raises(gguf.Invalid, match="inside its header"):
+        gguf.Gguf.parse(raw, 100)
+
+
+def test_a_file_is_read_in_growing_pieces(tmp_path):
+    path = tmp_path / "m.gguf"
+    path.write_bytes(sample())
+    whole = gguf.open(path)
+    small = gguf.open(path, first_read=16)
+    assert small.tensors == whole.tensors and small.keys() == whole.keys()
+    assert bytes(small.read(small.tensor("q"))) == bytes(range(68))
+    with pytest.raises(gguf.Invalid):
+        small.read(small.tensor("odd"))
+    with pytest.raises(gguf.Read):
+        gguf.open(tmp_path / "absent.gguf")
+    parsed = gguf.Gguf.parse(sample(), len(sample()))
+    with pytest.raises(gguf.Read):
+        parsed.read(parsed.tensor("q"))               # parsed from bytes: there is no file to read
+
+
+def test_every_value_type_and_its_conversions():
+    raw = w.file([("u8", w.U8, 200), ("i8", w.I8, -5), ("u16", w.U16, 60000), ("i16", w.I16, -300),
+                  ("u32", w.U32, 4000000000), ("i32", w.I32, -7), ("f32", w.F32, 0.5), ("yes", w.BOOL, 1),
+                  ("no", w.BOOL, 0), ("u64", w.U64, 2 ** 63 + 1), ("i64", w.I64, -2 ** 40), ("f64", w.F64, 1e300),
+                  ("ints", w.ARRAY, (w.I32, [3, -4, 5])), ("floats", w.ARRAY, (w.F32, [0.25, -2.0])),
+                  ("empty", w.ARRAY, (w.U8, [])), ("text", w.STRING, "")], [])
+    g = gguf.Gguf.parse(raw, len(raw))
+    assert [g.get(k) for k in ("u8", "i8", "u16", "i16", "u32", "i32")] == [200, -5, 60000, -300, 4000000000, -7]
+    assert (g.get("f32"), g.get("yes"), g.get("no"), g.get("u64"), g.get("i64"), g.get("f64")) == \
+        (0.5, True, False, 2 ** 63 + 1, -2 ** 40, 1e300)
+    assert g.get("ints") == [3, -4, 5] and g.get("floats") == [0.25, -2.0] and g.get("empty") == [] and g.get("text") == ""
+    # `as_u64` takes any integer that is not negative; `as_f64` only floats
+    from ctypes import byref, c_double, c_uint64
+    from loadngo_b200 import compute
+    L, v, d = compute.lib(), c_uint64(), c_double()
+    assert L.cc_gguf_get_u64(g._h, b"i16", -1, byref(v)) == 0
+    assert L.cc_gguf_get_u64(g._h, b"u8", -1, byref(v)) == 1 and v.value == 200
+    assert L.cc_gguf_get_u64(g._h, b"ints", 2, byref(v)) == 1 and v.value == 5
+    assert L.cc_gguf_get_u64(g._h, b"ints", 1, byref(v)) == 0
+    assert L.cc_gguf_get_u64(g._h, b"ints", 3, byref(v)) == 0
+    assert L.cc_gguf_get_f64(g._h, b"u32", -1, byref(d)) == 0
+    assert L.cc_gguf_get_f64(g._h, b"f64", -1, byref(d)) == 1 and d.value == 1e300
+
+
+@pytest.mark.parametrize("metadata, tensors, alignment, error, text", [
+    ([("a", w.ARRAY, (w.ARRAY, [(w.U8, [1])]))], [], 32, gguf.Invalid, "nested"),
+    ([("a", w.U8, 1), ("a", w.U8, 2)], [], 32, gguf.Invalid, "repeats"),
+    ([("flag", w.BOOL, 2)], [], 32, gguf.Invalid, "bool byte 2"),
+    ([("a", 13, b"\0\0\0\0")], [], 32, gguf.ValueType, "13"),
+    ([("bad", w.STRING, b"\xff\xfe")], [], 32, gguf.Utf8, "UTF-8"),
+    ([("bad", w.STRING, b"\xed\xa0\x80")], [], 32, gguf.Utf8, "UTF-8"),          # a surrogate
+    ([("bad", w.STRING, b"\xc0\x80")], [], 32, gguf.Utf8, "UTF-8"),              # an overlong form
+    ([("general.alignment", w.U32, 24)], [], 32, gguf.Invalid, "general.alignment"),
+    ([("general.alignment", w.STRING, "32")], [], 32, gguf.Invalid, "general.alignment"),
+    ([], [("t", [33], gguf.Q8_0, bytes(34))], 32, gguf.Invalid, "whole blocks of 32"),
+    ([], [("t", [16], gguf.MXFP4, bytes(17))], 32, gguf.Invalid, "whole blocks of 32"),
+    ([], [("t", [], gguf.F32, bytes(4))], 32, gguf.Invalid, "0 dimensions"),
+    ([], [("t", [1] * 9, gguf.F32, bytes(4))], 32, gguf.Invalid, "9 dimensions"),
+    ([], [("t", [2 ** 40, 2 ** 40], gguf.F32, bytes(4))], 32, gguf.Invalid, "overflows"),
+])
+def test_what_cannot_be_right_is_refused(metadata, tensors, alignment, error, text):
+    raw = w.file(metadata, tensors, alignment)
+    with pytest.raises(error, match=text):
+        gguf.Gguf.parse(raw, len(raw))
+
+
+def test_alignment_from_the_metadata_places_the_data():
+    raw = w.file([("general.alignment", w.U32, 64)],
+                 [("a", [2], gguf.BF16, bytes([1, 2, 3, 4])), ("b", [32], gguf.MXFP4, bytes(range(17)))], alignment=64)
+    g = gguf.Gguf.parse(raw, len(raw))
+    assert g.alignment == 64 and g.data_offset % 64 == 0
+    a, b = g.tensor("a"), g.tensor("b")
+    assert (a.len, b.len) == (4, 17) and b.offset - a.offset == 64
+    assert raw[b.offset:b.offset + 17] == bytes(range(17))
+    # an offset that is not a multiple of the alignment
+    wrong = w.file([], [("a", [2], gguf.BF16, bytes(4)), ("b", [32], gguf.MXFP4, bytes(17))], offsets=[0, 48])
+    with pytest.raises(gguf.Invalid, match="b: unaligned"):
+        gguf.Gguf.parse(wrong, len(wrong))
+
+
+def test_version_2_shares_the_layout():
+    raw = w.file([("k", w.U32, 7)], [("t", [4], gguf.F16, bytes(8))], version=2)
+    g = gguf.Gguf.parse(raw, len(raw))
+    assert g.version == 2 and g.get("k") == 7 and g.tensor("t").len == 8
+
+
+@pytest.mark.skipif(not os.path.exists(TINY), reason="the reference checkout is not mounted")
+def test_the_reference_tiny_model_reads_like_the_gguf_package_reads_it():
+    ref = pytest.importorskip("gguf")
+    theirs = ref.GGUFReader(TINY)
+    ours = gguf.open(TINY, first_read=512)           # the header is 5.6 KB: several doublings
+    assert ours.data_offset == theirs.data_offset and ours.alignment == theirs.alignment
+    for key, field in theirs.fields.items():
+        if key.startswith("GGUF."):
+            continue
+        want = field.contents()
+        got = ours.get(key)
+        assert got == pytest.approx(want) if isinstance(want, float) else got == want, key
+    assert [t.name for t in ours.tensors] == [t.name for t in theirs.tensors]
+    for mine, t in zip(ours.tensors, theirs.tensors):
+        assert mine.dims == [int(d) for d in t.shape] and mine.ggml_type == int(t.tensor_type)
+        assert mine.offset == t.data_offset and mine.len == t.n_bytes
+        assert np.array_equal(ours.read(mine), np.asarray(t.data).view(np.uint8).reshape(-1)), mine.name
