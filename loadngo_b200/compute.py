@@ -9,6 +9,7 @@ raises.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import os
 from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_float, c_int, c_int32,
@@ -586,4 +587,5 @@ class Batch:
             self._h = None
 
 
-_LIVE_CALLBACKS: list = []  # ctypes thunks must outlive the completion thread's call
+# ctypes thunks must outlive the completion thread's call; far fewer than this are ever pending
+_LIVE_CALLBACKS: collections.deque = collections.deque(maxlen=4096)

@@ -192,6 +192,10 @@ def main():
     block["embedded"] = np.stack([T["token_embd.weight"][t] for t in ids]).astype(np.float32)
     block["output_norm"] = T["output_norm.weight"].astype(np.float32)
     block["output_q8_0"] = T["output.weight:q8_0"]
+    # the embedding as stored and the prompt's token ids: with them the tests can write the whole
+    # model as a GGUF file again and load it the way the reference loads its fixture
+    block["token_embd_q8_0"] = T["token_embd.weight:q8_0"]
+    block["ids"] = np.array(ids, np.uint32)
     block["logits"] = want.astype(np.float32)
     block["meta"] = np.array(json.dumps({
         "layers": meta["gpt-oss.block_count"], "hidden": int(T["token_embd.weight"].shape[1]),
@@ -201,7 +205,8 @@ def main():
         "theta": meta["gpt-oss.rope.freq_base"], "factor": meta["gpt-oss.rope.scaling.factor"],
         "original_context": meta["gpt-oss.rope.scaling.original_context_length"], "positions": len(ids),
         "experts": meta["gpt-oss.expert_count"], "experts_used": meta["gpt-oss.expert_used_count"],
-        "expert_hidden": meta["gpt-oss.feed_forward_length"], "vocab": int(want.shape[1])}))
+        "expert_hidden": meta["gpt-oss.expert_feed_forward_length"], "vocab": int(want.shape[1]),
+        "feed_forward_length": meta["gpt-oss.feed_forward_length"], "context_length": meta["gpt-oss.context_length"]}))
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tiny_attention.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path} ({os.path.getsize(path)} bytes)")

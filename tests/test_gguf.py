@@ -9,7 +9,7 @@ import pytest
 
 from loadngo_b200 import gguf
 
-import gguf_writer as w
+from tests import gguf_writer as w
 
 TINY = "/root/reference/gpt-oss/tests/fixtures/tiny/model.gguf"
 
@@ -161,3 +161,40 @@ def test_the_reference_tiny_model_reads_like_the_gguf_package_reads_it():
         assert mine.dims == [int(d) for d in t.shape] and mine.ggml_type == int(t.tensor_type)
         assert mine.offset == t.data_offset and mine.len == t.n_bytes
         assert np.array_equal(ours.read(mine), np.asarray(t.data).view(np.uint8).reshape(-1)), mine.name
+
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_block.npz")
+
+
+def test_the_tiny_model_written_from_the_golden_vectors_gives_the_reference_shape(tmp_path):
+    """The model file the GPU tests load: its header parses, `Config.from_gguf` reads the shape the
+    reference's fixture has, and (where the reference checkout is present) every tensor's bytes
+    are the reference file's."""
+    import json
+    from loadngo_b200.gpt_oss import Config, ConfigError
+    golden = np.load(GOLDEN)
+    path = tmp_path / "tiny.gguf"
+    w.tiny_model(golden, path)
+    g = gguf.open(path, first_read=1024)
+    c = Config.from_gguf(g)
+    meta = json.loads(str(golden["meta"]))
+    assert (c.layers, c.hidden, c.heads, c.kv_heads, c.head_dim, c.window) == \
+        (meta["layers"], meta["hidden"], meta["heads"], meta["kv_heads"], meta["dim"], meta["window"]) == (4, 128, 4, 2, 32, 8)
+    assert (c.experts, c.experts_used, c.expert_hidden, c.vocab, c.context_length) == (4, 2, 64, 512, 2048)
+    assert (c.theta, c.factor, c.original_context) == (150000.0, 32.0, 64.0) and c.eps == float(np.float32(1e-5))
+    assert [c.is_sliding(l) for l in range(4)] == [True, False, True, False]
+    if os.path.exists(TINY):
+        theirs = gguf.open(TINY)
+        assert Config.from_gguf(theirs) == c
+        assert [(t.name, t.dims, t.ggml_type, t.len) for t in theirs.tensors] == \
+            [(t.name, t.dims, t.ggml_type, t.len) for t in g.tensors]
+        for mine, t in zip(g.tensors, theirs.tensors):
+            assert np.array_equal(g.read(mine), theirs.read(t)), t.name
+    # the refusals of config.rs:52-95
+    for drop, text in (("gpt-oss.block_count", "block_count is missing"), ("gpt-oss.rope.scaling.type", "YaRN")):
+        raw = path.read_bytes().replace(drop.encode(), drop.encode()[:-1] + b"_")
+        with pytest.raises(ConfigError, match=text):
+            Config.from_gguf(gguf.Gguf.parse(raw, len(raw)))
+    raw = path.read_bytes().replace(b"\x07\x00\x00\x00\x00\x00\x00\x00gpt-oss", b"\x07\x00\x00\x00\x00\x00\x00\x00gpt-0ss", 1)
+    with pytest.raises(ConfigError, match="architecture"):
+        Config.from_gguf(gguf.Gguf.parse(raw, len(raw)))
