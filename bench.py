@@ -162,8 +162,11 @@ def run_reference(args):
     lens = draw_lengths(SEQS_PER_GPU * args.gpus)
     step_bytes = algorithmic_bytes(lens + 1, 0) + algorithmic_bytes(lens + 1, WINDOW)
     # each "step" is one full step of the workload for the first sequences of the batch, as many
-    # as keep the whole run within a few minutes
-    sample = min(len(lens), 32)
+    # as keep the whole run of K steps within about a minute and a half: a pilot step over 32
+    # sequences gives the time per sequence
+    pilot = min(len(lens), 32)
+    pilot_s, _ = cpu_steps(lens[:pilot], cores, 0.0, min_steps=2)
+    sample = int(max(1, min(pilot, pilot * 90.0 / (max(args.steps, 1) * pilot_s))))
     sample_lens = lens[:sample]
     sample_bytes = algorithmic_bytes(sample_lens + 1, 0) + algorithmic_bytes(sample_lens + 1, WINDOW)
     for _ in range(args.warmup):
