@@ -381,6 +381,7 @@ struct cc_buffer {
     size_t len = 0;
     uint8_t *dev = nullptr;
     uint8_t *host = nullptr;       // pinned mirror, or null for device-only
+    uint8_t *host_alias = nullptr; // the mirror's address as kernels see it, or null if it is not mapped
     // byte ranges that differ between the two copies (empty when lo >= hi)
     size_t host_dirty_lo = 0, host_dirty_hi = 0;  // host newer than device
     size_t dev_dirty_lo = 0, dev_dirty_hi = 0;    // device newer than host
@@ -407,6 +408,7 @@ struct cc_gpu {
     cudaStream_t stream = nullptr;
     uint32_t *status_dev = nullptr;
     uint32_t *status_host = nullptr;  // pinned
+    uint32_t *status_host_alias = nullptr;  // as kernels see it, or null
     uint8_t *scratch = nullptr;       // decode workspace, grown on demand
     size_t scratch_bytes = 0;
     std::vector<uint8_t *> retired;   // outgrown workspaces: recorded batches may still name them
@@ -503,8 +505,13 @@ extern "C" int cc_gpu_new(int device, cc_gpu **out) {
     CUDA_TRY(cudaStreamCreateWithFlags(&gpu->stream, cudaStreamNonBlocking));
     CUDA_TRY(cudaMalloc(&gpu->status_dev, 256));
     CUDA_TRY(cudaMemset(gpu->status_dev, 0, 256));
-    CUDA_TRY(cudaMallocHost(&gpu->status_host, 256));
+    CUDA_TRY(cudaHostAlloc(&gpu->status_host, 256, cudaHostAllocMapped | cudaHostAllocPortable));
     *gpu->status_host = 0;
+    {
+        void *alias = nullptr;
+        if (cudaHostGetDevicePointer(&alias, gpu->status_host, 0) == cudaSuccess) gpu->status_host_alias = static_cast<uint32_t *>(alias);
+        else cudaGetLastError();
+    }
     gpu->watcher = std::thread(watcher_main, gpu);
     *out = gpu;
     return CC_OK;
@@ -550,16 +557,24 @@ int buffer_new(cc_gpu *gpu, size_t len, bool mirror, cc_buffer **out) {
     cc_buffer *b = new cc_buffer;
     b->gpu = gpu;
     b->len = len;
-    if (cudaMalloc(&b->dev, len) != cudaSuccess) {
+    // both copies are padded to 256 bytes: small copies between them round their ranges out to 16
+    const size_t padded = (len + 255) & ~static_cast<size_t>(255);
+    if (cudaMalloc(&b->dev, padded) != cudaSuccess) {
         cudaGetLastError();
         delete b;
         return fail(CC_ALLOC, "could not allocate a %zu-byte device buffer", len);
     }
-    if (mirror && cudaMallocHost(&b->host, len) != cudaSuccess) {
+    if (mirror && cudaHostAlloc(&b->host, padded, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
         cudaGetLastError();
         cudaFree(b->dev);
         delete b;
         return fail(CC_ALLOC, "could not allocate a %zu-byte pinned host mirror", len);
+    }
+    if (mirror) {
+        memset(b->host + len, 0, padded - len);
+        void *alias = nullptr;
+        if (cudaHostGetDevicePointer(&alias, b->host, 0) == cudaSuccess) b->host_alias = static_cast<uint8_t *>(alias);
+        else cudaGetLastError();
     }
     *out = b;
     return CC_OK;
@@ -1377,6 +1392,84 @@ extern "C" int cc_batch_read_back(cc_batch *b, cc_slice s) {
 
 namespace {
 
+// Small copies between host mirrors and device buffers.  A decode step moves a handful of ranges
+// of a few hundred bytes to a few hundred kilobytes each way; as separate cudaMemcpyAsync calls
+// each of them pays the copy engine's start-up on the stream, one after another.  Here all the
+// ranges of one direction go through one kernel that reads or writes the pinned, mapped host
+// memory directly over PCIe, sixteen bytes per thread and four loads in flight per thread.
+// Ranges larger than kKernelCopyLimit keep going to the copy engine.
+constexpr int kMaxRanges = 24;
+constexpr size_t kKernelCopyLimit = 2u << 20;
+struct CopyRange {
+    uint8_t *dst;
+    const uint8_t *src;
+    uint64_t chunks;   // of 16 bytes; both addresses are 16-byte aligned
+};
+struct CopyRanges {
+    CopyRange r[kMaxRanges];
+    uint32_t n;
+    uint32_t *status_dst;   // when set: *status_dst = *status_src; *status_src = 0 (the batch's status word)
+    uint32_t *status_src;
+};
+
+__global__ void __launch_bounds__(256) copy_ranges_kernel(const __grid_constant__ CopyRanges p) {
+    if (blockIdx.y < p.n) {
+        const CopyRange &r = p.r[blockIdx.y];
+        const uint4 *src = reinterpret_cast<const uint4 *>(r.src);
+        uint4 *dst = reinterpret_cast<uint4 *>(r.dst);
+        const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 256;
+        for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < r.chunks; i += 4 * stride) {
+            uint4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (i + k * stride < r.chunks) v[k] = src[i + k * stride];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (i + k * stride < r.chunks) dst[i + k * stride] = v[k];
+        }
+    }
+    if (p.status_dst && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+        *p.status_dst = *p.status_src;
+        *p.status_src = 0;
+    }
+}
+
+struct RangeList {
+    CopyRanges p{};
+    uint64_t most = 0;   // chunks of the longest range
+    void launch(cudaStream_t s) {
+        if (p.n == 0 && !p.status_dst) return;
+        uint64_t x = (most + 1023) / 1024;
+        if (x < 1) x = 1;
+        if (x > 64) x = 64;
+        copy_ranges_kernel<<<dim3(static_cast<unsigned>(x), p.n ? p.n : 1), 256, 0, s>>>(p);
+        p.n = 0;
+        p.status_dst = p.status_src = nullptr;
+        most = 0;
+    }
+    void add(uint8_t *dst, const uint8_t *src, size_t bytes, cudaStream_t s) {
+        if (p.n == kMaxRanges) launch(s);
+        p.r[p.n++] = CopyRange{dst, src, bytes / 16};
+        if (bytes / 16 > most) most = bytes / 16;
+    }
+};
+
+// One range of a buffer between its two copies, [lo, hi) rounded out to 16 bytes (the allocations
+// are padded and outside the range the copies agree): through `list` when the mirror is mapped and
+// the range is small, else by the copy engine.
+void copy_range(RangeList &list, cc_buffer *buf, size_t lo, size_t hi, bool to_device, cudaStream_t s) {
+    if (buf->host_alias && hi - lo <= kKernelCopyLimit) {
+        lo &= ~static_cast<size_t>(15);
+        hi = (hi + 15) & ~static_cast<size_t>(15);
+        if (to_device) list.add(buf->dev + lo, buf->host_alias + lo, hi - lo, s);
+        else list.add(buf->host_alias + lo, buf->dev + lo, hi - lo, s);
+    } else if (to_device) {
+        cudaMemcpyAsync(buf->dev + lo, buf->host + lo, hi - lo, cudaMemcpyHostToDevice, s);
+    } else {
+        cudaMemcpyAsync(buf->host + lo, buf->dev + lo, hi - lo, cudaMemcpyDeviceToHost, s);
+    }
+}
+
 // Uploads what the host changed, runs the recorded work, copies requested ranges back, and
 // queues the completion.  Consumes the batch.
 int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false, Pending *inline_job = nullptr) {
@@ -1396,13 +1489,14 @@ int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false, Pe
         return cuda_fail(e, "batch events");
     }
     cudaStream_t s = gpu->stream;
+    RangeList list;
     for (cc_buffer *buf : b->buffers) {
         if (buf->host && buf->host_dirty_lo < buf->host_dirty_hi) {
-            cudaMemcpyAsync(buf->dev + buf->host_dirty_lo, buf->host + buf->host_dirty_lo,
-                            buf->host_dirty_hi - buf->host_dirty_lo, cudaMemcpyHostToDevice, s);
+            copy_range(list, buf, buf->host_dirty_lo, buf->host_dirty_hi, true, s);
             buf->host_dirty_lo = buf->host_dirty_hi = 0;
         }
     }
+    list.launch(s);
     for (const cc_slice &o : b->outputs) {
         cc_buffer *buf = b->buffers[o.buffer];
         mark(buf->dev_dirty_lo, buf->dev_dirty_hi, o.offset, o.offset + o.len);
@@ -1445,13 +1539,20 @@ int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false, Pe
     }
     for (const cc_slice &rb : b->read_backs) {
         cc_buffer *buf = b->buffers[rb.buffer];
-        cudaMemcpyAsync(buf->host + rb.offset, buf->dev + rb.offset, rb.len, cudaMemcpyDeviceToHost, s);
+        copy_range(list, buf, rb.offset, rb.offset + rb.len, false, s);
         // what was copied back is clean again if it covers the whole dirty range
         if (rb.offset <= buf->dev_dirty_lo && rb.offset + rb.len >= buf->dev_dirty_hi)
             buf->dev_dirty_lo = buf->dev_dirty_hi = 0;
     }
-    cudaMemcpyAsync(gpu->status_host, gpu->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
-    cudaMemsetAsync(gpu->status_dev, 0, sizeof(uint32_t), s);
+    if (gpu->status_host_alias) {   // the status word travels with the last read-back launch
+        list.p.status_dst = gpu->status_host_alias;
+        list.p.status_src = gpu->status_dev;
+        list.launch(s);
+    } else {
+        list.launch(s);
+        cudaMemcpyAsync(gpu->status_host, gpu->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+        cudaMemsetAsync(gpu->status_dev, 0, sizeof(uint32_t), s);
+    }
     cudaEventRecord(job.end, s);
     if (inline_job) {   // the caller waits on its own thread: no trip through the completion thread
         *inline_job = std::move(job);
