@@ -5,7 +5,8 @@ Workload (the configuration the metric is quoted on): 32 ragged sequences per GP
 lengths uniform in [1024, 8192] (seed 0), 64 query heads over 8 KV heads of width 64, a paged
 bf16 KV cache of 16-token pages handed out in scattered order, sinks N(0,1).  One step = one new
 token per sequence through one full-causal layer and one 128-token sliding-window layer:
-fused RoPE + append, then decode attention, for each layer.  Positions advance every step.
+RoPE, append and decode attention, one launch per layer (`--unfused`: the RoPE + append kernel and
+the attention kernel as two).  Positions advance every step.
 
 Lines printed (rank 0): one JSON object with
   value    - algorithmic HBM GB/s of the whole job, inputs resident in HBM, timed with CUDA
@@ -191,7 +192,7 @@ def run_reference(args):
 
 def workload_config(gpus: int):
     return {"workload": "decode attention, gpt-oss-20b shapes: one new token per sequence through one "
-                        "full-causal and one 128-window layer (fused RoPE+append, then attention)",
+                        "full-causal and one 128-window layer (RoPE, append and attention of a layer in one launch)",
             "global_batch": SEQS_PER_GPU * gpus, "kv_len": f"uniform[{LEN_LO},{LEN_HI}] seed 0",
             "heads": "64q/8kv/hd64", "page_tokens": PAGE, "kv_cache": "paged bf16, scattered pages",
             "parallelism": f"kv-head x{gpus} (batch grows with N)",
@@ -205,7 +206,8 @@ class DecodeBench:
     """Both layers of the workload on one GPU, with every step's small inputs laid out ahead of
     time so that the resident run needs no host work between launches."""
 
-    def __init__(self, gpu, lens, kv_heads, total_steps):
+    def __init__(self, gpu, lens, kv_heads, total_steps, fused=True):
+        self.fused = fused
         from loadngo_b200 import compute
         from loadngo_b200.layer import PagedAttentionLayer
         from oracle import oracle  # only for bf16 rounding of the synthetic inputs
@@ -277,8 +279,14 @@ class DecodeBench:
         S = lambda i, off, ln: c.Slice(base + i, off, ln)
         cache = c.PagedCache(S(layer.POOL, 0, len(layer.cache.pool)), S(layer.BT, 0, len(layer.cache.table)),
                              layer.cache.max_pages, 0, g)
-        batch.rope_append_paged((S(layer.Q, 0, n * h * D * 2), S(layer.K, 0, n * g * D * 2), S(layer.V, 0, n * g * D * 2)),
-                                False, S(layer.QROT, 0, 2 * n * h * D * 2), S(layer.TABLE, 0, len(layer.table)), 0,
+        qkv = (S(layer.Q, 0, n * h * D * 2), S(layer.K, 0, n * g * D * 2), S(layer.V, 0, n * g * D * 2))
+        if self.fused:   # rotation, append and attention of the step in one launch
+            batch.attention_decode_step_paged(qkv, False, S(layer.TABLE, 0, len(layer.table)), 0, cache,
+                                              S(layer.LENS, step * n * 4, n * 4), n, int(self.len_all[step].max()),
+                                              S(layer.SINKS, 0, h * 4), layer.window, layer.scale,
+                                              S(layer.OUT, 0, n * h * D * 2))
+            return
+        batch.rope_append_paged(qkv, False, S(layer.QROT, 0, 2 * n * h * D * 2), S(layer.TABLE, 0, len(layer.table)), 0,
                                 S(layer.POS, step * n * 4, n * 4), S(layer.SEQ, 0, n * 4), cache, n)
         batch.attention_decode_paged(S(layer.QROT, 0, 2 * n * h * D * 2), cache, S(layer.LENS, step * n * 4, n * 4), n,
                                      int(self.len_all[step].max()), S(layer.SINKS, 0, h * 4), layer.window,
@@ -293,7 +301,9 @@ class DecodeBench:
         batch = self.gpu.batch(self.all_buffers())
         nb = len(self.layers[0].buffers())
         for i in range(steps):
-            if only_full_decode:
+            if only_full_decode and self.fused:
+                self.record_step(batch, 0, first_step, 0)
+            elif only_full_decode:
                 c, layer = self.compute, self.layers[0]
                 n, h, g = self.seqs, self.heads, self.kv_heads
                 S = lambda j, off, ln: c.Slice(j, off, ln)
@@ -538,8 +548,14 @@ def run_longctx(args):
                 cache = compute.PagedCache(S(layer.POOL, 0, len(layer.cache.pool)), S(layer.BT, 0, len(layer.cache.table)),
                                            layer.cache.max_pages, 0, kvl)
                 n = seqs
-                batch.rope_append_paged((S(layer.Q, 0, n * heads * D * 2), S(layer.K, 0, n * kvl * D * 2),
-                                         S(layer.V, 0, n * kvl * D * 2)), False, S(layer.QROT, 0, 2 * n * heads * D * 2),
+                qkv = (S(layer.Q, 0, n * heads * D * 2), S(layer.K, 0, n * kvl * D * 2), S(layer.V, 0, n * kvl * D * 2))
+                if not args.unfused:
+                    batch.attention_decode_step_paged(qkv, False, S(layer.TABLE, 0, len(layer.table)), 0, cache,
+                                                      S(layer.LENS, step * n * 4, n * 4), n, int(lens.max()) + step + 1,
+                                                      S(layer.SINKS, 0, heads * 4), layer.window, layer.scale,
+                                                      S(layer.OUT, 0, n * heads * D * 2))
+                    continue
+                batch.rope_append_paged(qkv, False, S(layer.QROT, 0, 2 * n * heads * D * 2),
                                         S(layer.TABLE, 0, len(layer.table)), 0, S(layer.POS, step * n * 4, n * 4),
                                         S(layer.SEQ, 0, n * 4), cache, n)
                 batch.attention_decode_paged(S(layer.QROT, 0, 2 * n * heads * D * 2), cache,
@@ -813,7 +829,7 @@ def run_gpu(args):
         return
     lens = draw_lengths(SEQS_PER_GPU * world)
     total_steps = args.warmup + args.steps
-    bench = DecodeBench(gpu, lens, len(heads_here), total_steps * 3 + 2)
+    bench = DecodeBench(gpu, lens, len(heads_here), total_steps * 3 + 2, fused=not args.unfused)
 
     # ---- resident run: `value` ----------------------------------------------------------
     bench.resident_run(0, args.warmup)
@@ -833,6 +849,17 @@ def run_gpu(args):
     full_bytes = algorithmic_bytes(bench.len_all[total_steps].astype(np.int64), 0, bench.kv_heads)
     achieved = full_bytes / (k_s / reps) / 1e9
     peak, peak_kind = measured_peak()
+    attention_only = None
+    if bench.fused:   # the same launch without the rotation and the append in it, for comparison
+        bench.fused = False
+        bench.resident_run(total_steps, 1)    # fills the rotated-query planes that kernel reads
+        bench.resident_run(total_steps, 3, only_full_decode=True)
+        a_s, _ = bench.resident_run(total_steps, reps, only_full_decode=True)
+        bench.fused = True
+        attention_only = {"us_per_launch": a_s / reps * 1e6, "achieved": full_bytes / (a_s / reps) / 1e9,
+                          "frac": full_bytes / (a_s / reps) / 1e9 / peak,
+                          "note": "decode attention alone on rotated queries (the kernel `--unfused` launches after "
+                                  "its RoPE + append kernel), same bytes"}
 
     # ---- end to end through host buffers ---------------------------------------------------
     base = total_steps + 1
@@ -875,13 +902,17 @@ def run_gpu(args):
             "clocks": clock,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_s / args.steps * 1e3, "timed_with": "host clock around K steps, synchronised"},
-            "roofline": {"bound": "hbm", "kernel": "decode_kernel (full-causal layer)", "achieved": achieved,
+            "roofline": {"bound": "hbm",
+                         "kernel": "decode_kernel<fused> (full-causal layer: RoPE, append and attention)" if bench.fused
+                         else "decode_kernel (full-causal layer)", "achieved": achieved,
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                          "traffic": int(full_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
                          "traffic_source": "ncu capture of a smaller launch, scaled by algorithmic bytes",
                          "algorithmic_bytes_per_launch": full_bytes,
                          "us_per_launch": k_s / reps * 1e6},
         }
+        if attention_only is not None:
+            line["roofline"]["attention_only"] = attention_only
         if prefill is not None:
             line["prefill"] = prefill
         if world == 1 and not args.no_cpu:
@@ -909,6 +940,8 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "longctx", "block", "q8_0"],
                     help="decode: the headline (config 2); longctx: config 4; block: config 5; q8_0: the "
                          "projections as shipped")
+    ap.add_argument("--unfused", action="store_true",
+                    help="decode steps as two launches per layer (RoPE + append, then attention) instead of one")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (config 3) section")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill (config 3) section")

@@ -142,6 +142,29 @@ int cc_attention_decode_paged(void *stream, const cc_decode_args *args);
 size_t cc_decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_seq_len, uint32_t window,
                                  uint32_t pages_per_split);
 
+/* A whole decode step of one layer in one launch: what cc_rope_append_paged followed by
+ * cc_attention_decode_paged do for one new token per sequence (gpt-oss/src/gpu.rs:741-806 with
+ * n = 1: rotate_halves on Q and K, the copy_rows pair, attention), without the launch in between
+ * and without the rotated query's trip through memory.  Sequence i's new token sits at position
+ * attn.seq_lens[i] - 1; its rotated key and its value are written into the page that position
+ * belongs to (and are used by this launch), its rotated query is formed in registers with the
+ * same arithmetic and the same hi + lo split.  attn.q_hi and attn.q_lo are not read (may be NULL);
+ * attn.pool must be writable.  Results are bit-identical to the two separate calls. */
+typedef struct cc_decode_step_args {
+    cc_decode_args attn;
+    const void *q;             /* [seqs][heads][64] raw (before rotation) */
+    const void *k;             /* [seqs][kv_heads][64] */
+    const void *v;             /* [seqs][kv_heads][64] */
+    uint32_t in_f32;           /* 0: q, k, v are bfloat16; 1: float */
+    const float *table;        /* (cos, sin) pairs from cc_rope_table, row = position - table_start */
+    uint64_t table_start;
+    uint64_t table_rows;
+    uint32_t q_row_stride;     /* elements between sequences' rows; 0 = packed */
+    uint32_t k_row_stride;
+    uint32_t v_row_stride;
+} cc_decode_step_args;
+int cc_attention_decode_step_paged(void *stream, const cc_decode_step_args *args);
+
 /* The same decode attention for callers that must not allocate device memory.  It has no
  * counterpart in loadngo: metal-compute allocates freely from unified memory.  Who needs it: a
  * host that gave all of HBM to its page pool and weights at start-up (a later cudaMalloc would
@@ -398,6 +421,12 @@ int cc_batch_rope_append_paged(cc_batch *batch, cc_slice q, cc_slice k, cc_slice
 int cc_batch_attention_decode_paged(cc_batch *batch, cc_slice q_rot, const cc_paged_cache *cache,
                                     cc_slice seq_lens, uint32_t seqs, uint32_t max_seq_len, const cc_slice *sinks,
                                     uint32_t window, float scale, cc_slice out);
+/* cc_attention_decode_step_paged as a dispatch: q, k, v raw rows of the `seqs` new tokens; writes
+ * `out` and the cache's pool. */
+int cc_batch_attention_decode_step_paged(cc_batch *batch, cc_slice q, cc_slice k, cc_slice v, uint32_t in_f32,
+                                         cc_slice table, uint64_t table_start, const cc_paged_cache *cache,
+                                         cc_slice seq_lens, uint32_t seqs, uint32_t max_seq_len,
+                                         const cc_slice *sinks, uint32_t window, float scale, cc_slice out);
 int cc_batch_attention_prefill_paged(cc_batch *batch, cc_slice q_rot, const cc_paged_cache *cache,
                                      cc_slice q_offsets, cc_slice starts, uint32_t seqs, uint32_t total_tokens,
                                      uint32_t max_t, const cc_slice *sinks, uint32_t window, float scale,

@@ -107,6 +107,13 @@ class DecodeArgs(Structure):
                 ("pages_per_split", c_uint32), ("status", c_void_p)]
 
 
+class DecodeStepArgs(Structure):
+    """`cc_decode_step_args`: the fused decode step."""
+    _fields_ = [("attn", DecodeArgs), ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("in_f32", c_uint32),
+                ("table", c_void_p), ("table_start", c_uint64), ("table_rows", c_uint64),
+                ("q_row_stride", c_uint32), ("k_row_stride", c_uint32), ("v_row_stride", c_uint32)]
+
+
 class PrefillArgs(Structure):
     _fields_ = [("q_hi", c_void_p), ("q_lo", c_void_p), ("pool", c_void_p), ("pool_pages", c_uint32),
                 ("block_table", c_void_p), ("max_pages", c_uint32), ("ring_pages", c_uint32),
@@ -138,6 +145,7 @@ SYMBOLS = {
     "cc_rope_append_paged": (c_int, [c_void_p, POINTER(RopeAppendArgs)]),
     "cc_attention_decode_paged": (c_int, [c_void_p, POINTER(DecodeArgs)]),
     "cc_decode_workspace_bytes": (c_size_t, [c_uint32, c_uint32, c_uint32, c_uint32, c_uint32]),
+    "cc_attention_decode_step_paged": (c_int, [c_void_p, POINTER(DecodeStepArgs)]),
     "cc_attention_prefill_paged": (c_int, [c_void_p, POINTER(PrefillArgs)]),
     "cc_attention_decode_paged_static": (c_int, [c_void_p, POINTER(DecodeArgs)]),
     "cc_decode_static_scratch_bytes": (c_size_t, []),
@@ -209,6 +217,9 @@ SYMBOLS = {
                                            c_uint64, Slice, Slice, POINTER(PagedCache), c_uint32]),
     "cc_batch_attention_decode_paged": (c_int, [c_void_p, Slice, POINTER(PagedCache), Slice, c_uint32,
                                                 c_uint32, POINTER(Slice), c_uint32, c_float, Slice]),
+    "cc_batch_attention_decode_step_paged": (c_int, [c_void_p, Slice, Slice, Slice, c_uint32, Slice, c_uint64,
+                                                     POINTER(PagedCache), Slice, c_uint32, c_uint32, POINTER(Slice),
+                                                     c_uint32, c_float, Slice]),
     "cc_batch_attention_prefill_paged": (c_int, [c_void_p, Slice, POINTER(PagedCache), Slice, Slice,
                                                  c_uint32, c_uint32, c_uint32, POINTER(Slice),
                                                  c_uint32, c_float, Slice]),
@@ -532,6 +543,15 @@ class Batch:
                                max_seq_len: int, sinks, window: int, scale: float, out: Slice) -> None:
         check(lib().cc_batch_attention_decode_paged(self._h, q_rot, byref(cache), seq_lens, seqs,
                                                     max_seq_len, _opt(sinks), window, scale, out))
+
+    def attention_decode_step_paged(self, qkv, in_f32: bool, table: Slice, table_start: int, cache: PagedCache,
+                                    seq_lens: Slice, seqs: int, max_seq_len: int, sinks, window: int, scale: float,
+                                    out: Slice) -> None:
+        """RoPE, append and decode attention for one new token per sequence in one launch."""
+        q, k, v = qkv
+        check(lib().cc_batch_attention_decode_step_paged(self._h, q, k, v, 1 if in_f32 else 0, table, table_start,
+                                                         byref(cache), seq_lens, seqs, max_seq_len, _opt(sinks), window,
+                                                         scale, out))
 
     def attention_prefill_paged(self, q_rot: Slice, cache: PagedCache, q_offsets: Slice, starts: Slice,
                                 seqs: int, total_tokens: int, max_t: int, sinks, window: int,

@@ -260,12 +260,12 @@ extern "C" size_t cc_decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, ui
 
 namespace {
 // Validates, builds the tensor map and the kernel arguments; launches nothing.
-int decode_prepare(const cc_decode_args *a, cc::DecodeParams *out) {
+int decode_prepare(const cc_decode_args *a, cc::DecodeParams *out, bool fused = false) {
     if (!a) return fail(CC_DISPATCH, "decode: null arguments");
     if (int rc = check_heads("decode", a->heads, a->kv_heads)) return rc;
     if (a->seqs == 0 || a->seqs > 65535) return fail(CC_DISPATCH, "decode: %u sequences (1..65535)", a->seqs);
     if (a->kv_heads > 65535) return fail(CC_DISPATCH, "decode: %u key/value heads", a->kv_heads);
-    if (!a->q_hi || !a->pool || !a->block_table || !a->seq_lens || !a->out || !a->workspace)
+    if ((!fused && !a->q_hi) || !a->pool || !a->block_table || !a->seq_lens || !a->out || !a->workspace)
         return fail(CC_DISPATCH, "decode: null pointer");
     if (a->max_seq_len == 0 || a->max_pages == 0 || a->pool_pages == 0)
         return fail(CC_DISPATCH, "decode: empty sequence bound, block table or pool");
@@ -280,7 +280,8 @@ int decode_prepare(const cc_decode_args *a, cc::DecodeParams *out) {
     } else if (div_up(a->max_seq_len, cc::kPageTokens) > a->max_pages) {
         return fail(CC_DISPATCH, "decode: %u keys need more than %u pages per sequence", a->max_seq_len, a->max_pages);
     }
-    for (const void *ptr : {a->q_hi, a->q_lo, (const void *)a->out, (const void *)a->workspace})
+    for (const void *ptr : {fused ? nullptr : a->q_hi, fused ? nullptr : a->q_lo, (const void *)a->out,
+                            (const void *)a->workspace})
         if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(CC_DISPATCH, "decode: pointer not 16-byte aligned");
     const uint32_t pages = visible_pages(a->max_seq_len, a->window);
     const uint32_t pps = choose_pages_per_split(a->seqs, a->kv_heads, pages, a->pages_per_split);
@@ -290,8 +291,8 @@ int decode_prepare(const cc_decode_args *a, cc::DecodeParams *out) {
         return fail(CC_DISPATCH, "decode: workspace of %zu bytes, need %zu", a->workspace_bytes, need);
     cc::DecodeParams p{};
     if (int rc = make_pool_map(&p.pool_map, a->pool, a->pool_pages, a->kv_heads, cc::kTileRows)) return rc;
-    p.q_hi = static_cast<const uint16_t *>(a->q_hi);
-    p.q_lo = static_cast<const uint16_t *>(a->q_lo);
+    p.q_hi = fused ? nullptr : static_cast<const uint16_t *>(a->q_hi);
+    p.q_lo = fused ? nullptr : static_cast<const uint16_t *>(a->q_lo);
     p.block_table = a->block_table;
     p.seq_lens = a->seq_lens;
     p.sinks = a->sinks;
@@ -321,6 +322,40 @@ extern "C" int cc_attention_decode_paged(void *stream, const cc_decode_args *a) 
     if (int rc = decode_prepare(a, &p)) return rc;
     cc::launch_decode(p, static_cast<cudaStream_t>(stream));
     return launch_status("decode launch");
+}
+
+namespace {
+// The fused step: the attention arguments as for decode, plus the new token's raw rows.
+int decode_step_prepare(const cc_decode_step_args *a, cc::DecodeParams *out) {
+    if (!a) return fail(CC_DISPATCH, "decode step: null arguments");
+    cc::DecodeParams p;
+    if (int rc = decode_prepare(&a->attn, &p, true)) return rc;
+    if (!a->q || !a->k || !a->v || !a->table) return fail(CC_DISPATCH, "decode step: null pointer");
+    if (a->table_rows == 0) return fail(CC_DISPATCH, "decode step: empty rotary table");
+    for (const void *ptr : {a->q, a->k, a->v, (const void *)a->table, a->attn.pool})
+        if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(CC_DISPATCH, "decode step: pointer not 16-byte aligned");
+    p.q_new = a->q; p.k_new = a->k; p.v_new = a->v;
+    p.in_f32 = a->in_f32 ? 1 : 0;
+    p.table = a->table;
+    p.table_start = static_cast<int64_t>(a->table_start);
+    p.table_rows = static_cast<int64_t>(a->table_rows);
+    p.q_stride = a->q_row_stride ? a->q_row_stride : a->attn.heads * cc::kHeadDim;
+    p.k_stride = a->k_row_stride ? a->k_row_stride : a->attn.kv_heads * cc::kHeadDim;
+    p.v_stride = a->v_row_stride ? a->v_row_stride : a->attn.kv_heads * cc::kHeadDim;
+    if (p.q_stride < a->attn.heads * cc::kHeadDim || p.k_stride < a->attn.kv_heads * cc::kHeadDim ||
+        p.v_stride < a->attn.kv_heads * cc::kHeadDim || p.q_stride % 8 || p.k_stride % 8 || p.v_stride % 8)
+        return fail(CC_DISPATCH, "decode step: row strides must cover a row and be multiples of 8 elements");
+    p.pool = static_cast<uint16_t *>(const_cast<void *>(a->attn.pool));
+    *out = p;
+    return CC_OK;
+}
+}  // namespace
+
+extern "C" int cc_attention_decode_step_paged(void *stream, const cc_decode_step_args *a) {
+    cc::DecodeParams p;
+    if (int rc = decode_step_prepare(a, &p)) return rc;
+    cc::launch_decode(p, static_cast<cudaStream_t>(stream));
+    return launch_status("decode step launch");
 }
 
 
@@ -1278,6 +1313,30 @@ extern "C" int cc_batch_rope_append_paged(cc_batch *b, cc_slice q, cc_slice k, c
     return CC_OK;
 }
 
+namespace {
+// The gpu's decode scratch grows while recording, so that commit itself never allocates.
+int grow_decode_scratch(cc_gpu *gpu, uint32_t seqs, uint32_t kv_heads, uint32_t max_seq_len, uint32_t window,
+                        cc_decode_args *a) {
+    const size_t need = cc_decode_workspace_bytes(seqs, kv_heads, max_seq_len, window, 0);
+    if (gpu->scratch_bytes < need) {
+        cudaSetDevice(gpu->device);
+        const size_t grow = need + need / 2;
+        uint8_t *fresh = nullptr;
+        if (cudaMalloc(&fresh, grow) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(CC_ALLOC, "could not allocate %zu bytes of decode scratch", grow);
+        }
+        CUDA_TRY(cudaMemset(fresh, 0, grow));
+        if (gpu->scratch) gpu->retired.push_back(gpu->scratch);
+        gpu->scratch = fresh;
+        gpu->scratch_bytes = grow;
+    }
+    a->workspace = gpu->scratch;
+    a->workspace_bytes = gpu->scratch_bytes;
+    return CC_OK;
+}
+}  // namespace
+
 extern "C" int cc_batch_attention_decode_paged(cc_batch *b, cc_slice q_rot, const cc_paged_cache *cache,
                                                cc_slice seq_lens, uint32_t seqs, uint32_t max_seq_len,
                                                const cc_slice *sinks, uint32_t window, float scale, cc_slice out) {
@@ -1308,24 +1367,7 @@ extern "C" int cc_batch_attention_decode_paged(cc_batch *b, cc_slice q_rot, cons
     a.out = po;
     a.pages_per_split = 0;
     a.status = b->gpu->status_dev;
-    // The gpu's scratch grows here, while recording, so that commit itself never allocates.
-    const size_t need = cc_decode_workspace_bytes(seqs, cache->kv_heads, max_seq_len, window, 0);
-    cc_gpu *gpu = b->gpu;
-    if (gpu->scratch_bytes < need) {
-        cudaSetDevice(gpu->device);
-        const size_t grow = need + need / 2;
-        uint8_t *fresh = nullptr;
-        if (cudaMalloc(&fresh, grow) != cudaSuccess) {
-            cudaGetLastError();
-            return fail(CC_ALLOC, "could not allocate %zu bytes of decode scratch", grow);
-        }
-        CUDA_TRY(cudaMemset(fresh, 0, grow));
-        if (gpu->scratch) gpu->retired.push_back(gpu->scratch);
-        gpu->scratch = fresh;
-        gpu->scratch_bytes = grow;
-    }
-    a.workspace = gpu->scratch;
-    a.workspace_bytes = gpu->scratch_bytes;
+    if (int rc = grow_decode_scratch(b->gpu, seqs, cache->kv_heads, max_seq_len, window, &a)) return rc;
     cc::DecodeParams p;
     if (int rc = decode_prepare(&a, &p)) return rc;
     b->work.push_back([=](cudaStream_t s) {
@@ -1333,6 +1375,59 @@ extern "C" int cc_batch_attention_decode_paged(cc_batch *b, cc_slice q_rot, cons
         return launch_status("decode launch");
     });
     wrote(b, out);
+    ++b->dispatches;
+    return CC_OK;
+}
+
+extern "C" int cc_batch_attention_decode_step_paged(cc_batch *b, cc_slice q, cc_slice k, cc_slice v, uint32_t in_f32,
+                                                    cc_slice table, uint64_t table_start, const cc_paged_cache *cache,
+                                                    cc_slice seq_lens, uint32_t seqs, uint32_t max_seq_len,
+                                                    const cc_slice *sinks, uint32_t window, float scale, cc_slice out) {
+    if (!b) return fail(CC_DISPATCH, "decode step: null batch");
+    if (seqs == 0) return fail(CC_DISPATCH, "decode step: nothing to do");
+    uint8_t *pool, *bt;
+    uint32_t pool_pages, rows;
+    if (int rc = check_cache(b, cache, seqs, &pool, &pool_pages, &bt, &rows)) return rc;
+    const uint64_t heads = static_cast<uint64_t>(cache->kv_heads) * cc::kGroup;
+    const uint64_t esz = in_f32 ? 4 : 2;
+    uint8_t *pq, *pk, *pv, *pt, *pl, *po, *ps = nullptr;
+    if (int rc = check(b, "q", q, seqs * heads * 64 * esz, 16, &pq)) return rc;
+    if (int rc = check(b, "k", k, static_cast<uint64_t>(seqs) * cache->kv_heads * 64 * esz, 16, &pk)) return rc;
+    if (int rc = check(b, "v", v, static_cast<uint64_t>(seqs) * cache->kv_heads * 64 * esz, 16, &pv)) return rc;
+    if (table.len == 0 || table.len % 256 != 0) return fail(CC_DISPATCH, "table: %llu bytes is not rows of 32 pairs",
+                                                            (unsigned long long)table.len);
+    if (int rc = check(b, "table", table, table.len, 16, &pt)) return rc;
+    if (int rc = check(b, "seq_lens", seq_lens, static_cast<uint64_t>(seqs) * 4, 4, &pl)) return rc;
+    if (int rc = check(b, "out", out, seqs * heads * 64 * 2, 16, &po)) return rc;
+    if (sinks)
+        if (int rc = check(b, "sinks", *sinks, heads * 4, 4, &ps)) return rc;
+    if (int rc = check_output(b, out, {&q, &k, &v, &table, &cache->pool, &cache->block_table, &seq_lens, sinks})) return rc;
+    if (int rc = check_output(b, cache->pool, {&q, &k, &v, &table, &cache->block_table, &seq_lens, sinks, &out})) return rc;
+    cc_decode_step_args a{};
+    a.attn.pool = pool; a.attn.pool_pages = pool_pages;
+    a.attn.block_table = reinterpret_cast<const int32_t *>(bt);
+    a.attn.max_pages = cache->max_pages; a.attn.ring_pages = cache->ring_pages;
+    a.attn.seq_lens = reinterpret_cast<const int32_t *>(pl);
+    a.attn.seqs = seqs; a.attn.max_seq_len = max_seq_len;
+    a.attn.sinks = reinterpret_cast<const float *>(ps);
+    a.attn.heads = static_cast<uint32_t>(heads); a.attn.kv_heads = cache->kv_heads;
+    a.attn.window = window; a.attn.scale = scale;
+    a.attn.out = po;
+    a.attn.pages_per_split = 0;
+    a.attn.status = b->gpu->status_dev;
+    a.q = pq; a.k = pk; a.v = pv; a.in_f32 = in_f32;
+    a.table = reinterpret_cast<const float *>(pt);
+    a.table_start = table_start;
+    a.table_rows = table.len / 256;
+    if (int rc = grow_decode_scratch(b->gpu, seqs, cache->kv_heads, max_seq_len, window, &a.attn)) return rc;
+    cc::DecodeParams p;
+    if (int rc = decode_step_prepare(&a, &p)) return rc;
+    b->work.push_back([=](cudaStream_t s) {
+        cc::launch_decode(p, s);
+        return launch_status("decode step launch");
+    });
+    wrote(b, out);
+    if (b->buffers[cache->pool.buffer]->host) wrote(b, cache->pool);  // a mirrored pool is read back lazily, whole
     ++b->dispatches;
     return CC_OK;
 }

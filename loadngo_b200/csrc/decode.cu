@@ -35,6 +35,33 @@ constexpr int kSmemBytes = kWarps * kWarpBytes + 1024 /*align*/ + 256 /*barriers
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 
+// One raw input element pair (elements e, e + 1; e even) of a row, widened.
+template <bool F32>
+__device__ __forceinline__ float2 load_pair(const void *row, int e) {
+    if constexpr (F32) {
+        return *reinterpret_cast<const float2 *>(static_cast<const float *>(row) + e);
+    } else {
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(row) + e);
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+}
+__device__ __forceinline__ float load_one(const void *row, int e, bool f32) {
+    return f32 ? static_cast<const float *>(row)[e]
+               : __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t *>(row)[e]) << 16);
+}
+// The reference's rotation (gpt-oss/src/model.rs:397-402): separately rounded products.
+__device__ __forceinline__ void rotate(float &a, float &b, float c, float s) {
+    const float a0 = a, b0 = b;
+    a = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(b0, s));
+    b = __fadd_rn(__fmul_rn(b0, c), __fmul_rn(a0, s));
+}
+// hi = bf16(x), lo = bf16(x - hi), two elements at a time.
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t &hi, uint32_t &lo) {
+    hi = pack_bf16x2(x0, x1);
+    lo = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
+}
+
+template <bool kFused>
 __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -84,8 +111,11 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_consta
         return (it < count && idx < p.max_pages) ? table_row[idx] : -1;
     };
     const int32_t entry0 = table_entry(lane), entry1 = table_entry(lane + 32);
+    auto page_of = [&](int it) -> int32_t {   // called by the whole warp
+        return it < 64 ? __shfl_sync(0xffffffffu, it < 32 ? entry0 : entry1, it & 31) : table_entry(it);
+    };
     auto issue = [&](int it) {   // called by the whole warp
-        int32_t page = it < 64 ? __shfl_sync(0xffffffffu, it < 32 ? entry0 : entry1, it & 31) : table_entry(it);
+        int32_t page = page_of(it);
         if (lane != 0) return;
         if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages) {
             raise_status(p.status, kStatusBadPage);
@@ -101,7 +131,52 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_consta
     // Query fragments: row r (0-7) = head r "hi", row r + 8 = the same head's "lo".
     const int hr = lane >> 2, tq = lane & 3;
     uint32_t qa[4][4];
-    {
+    const float *cs_row = nullptr;   // fused: the new position's (cos, sin) pairs
+    // fused: the new position's rotated key (elements lane and lane + 32) and value (elements 2 lane,
+    // 2 lane + 1) as bf16, held by the warp that will meet the page they belong to; fetched here,
+    // behind the first copies, so that the last tile does not wait for them
+    uint32_t new_k = 0, new_v = 0;
+    if constexpr (kFused) {
+        int64_t row = static_cast<int64_t>(L) - 1 - p.table_start;
+        if (row < 0 || row >= p.table_rows) {
+            if (tid == 0) raise_status(p.status, kStatusBadTableRow);
+            row = 0;   // stay inside the table; the status marks the result invalid
+        }
+        cs_row = p.table + row * kHeadDim;
+        // Head hr's raw q: this lane's fragment elements are d = ks*16 + {2tq, 2tq+1, 8+2tq, 9+2tq};
+        // element d < 32 turns with element d + 32, which is the same slot of ks + 2.
+        const size_t elem = static_cast<size_t>(b) * p.q_stride + (static_cast<size_t>(g) * kGroup + hr) * kHeadDim;
+        const void *qrow = p.in_f32 ? static_cast<const void *>(static_cast<const float *>(p.q_new) + elem)
+                                    : static_cast<const void *>(static_cast<const uint16_t *>(p.q_new) + elem);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int d = ks * 16 + j * 8 + 2 * tq;
+                float2 a = p.in_f32 ? load_pair<true>(qrow, d) : load_pair<false>(qrow, d);
+                float2 c = p.in_f32 ? load_pair<true>(qrow, d + 32) : load_pair<false>(qrow, d + 32);
+                const float4 e = *reinterpret_cast<const float4 *>(cs_row + 2 * d);   // cos, sin, cos, sin
+                rotate(a.x, c.x, e.x, e.y);
+                rotate(a.y, c.y, e.z, e.w);
+                split_pair(a.x, a.y, qa[ks][2 * j], qa[ks][2 * j + 1]);
+                split_pair(c.x, c.y, qa[ks + 2][2 * j], qa[ks + 2][2 * j + 1]);
+            }
+        }
+        if (split == splits - 1 && ((page_hi - p0) & (kWarps - 1)) == warp) {
+            const size_t kelem = static_cast<size_t>(b) * p.k_stride + static_cast<size_t>(g) * kHeadDim;
+            const size_t velem = static_cast<size_t>(b) * p.v_stride + static_cast<size_t>(g) * kHeadDim;
+            const void *krow = p.in_f32 ? static_cast<const void *>(static_cast<const float *>(p.k_new) + kelem)
+                                        : static_cast<const void *>(static_cast<const uint16_t *>(p.k_new) + kelem);
+            const void *vrow = p.in_f32 ? static_cast<const void *>(static_cast<const float *>(p.v_new) + velem)
+                                        : static_cast<const void *>(static_cast<const uint16_t *>(p.v_new) + velem);
+            float ka = load_one(krow, lane, p.in_f32), kb2 = load_one(krow, lane + 32, p.in_f32);
+            const float2 e = *reinterpret_cast<const float2 *>(cs_row + 2 * lane);
+            rotate(ka, kb2, e.x, e.y);
+            new_k = pack_bf16x2(ka, kb2);   // element lane in the low half, lane + 32 in the high
+            const float2 vv = p.in_f32 ? load_pair<true>(vrow, 2 * lane) : load_pair<false>(vrow, 2 * lane);
+            new_v = pack_bf16x2(vv.x, vv.y);
+        }
+    } else {
         const size_t qrow = out_base + static_cast<size_t>(hr) * kHeadDim;
         const uint32_t *qh = reinterpret_cast<const uint32_t *>(p.q_hi + qrow);
         const uint32_t *ql = p.q_lo ? reinterpret_cast<const uint32_t *>(p.q_lo + qrow) : nullptr;
@@ -134,6 +209,30 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_consta
             break;
         }
         const uint32_t tile = my_tiles_u32 + stage * kTileBytes;
+        if constexpr (kFused) {
+            // The page that takes the new position: its K and V rows are written here, into the tile
+            // that has just arrived (whatever the pool held in that row) and into the pool for the
+            // steps to come.  One warp of one CTA per (sequence, KV head) gets here.
+            if (p0 + warp + it * kWarps == page_hi) {
+                int32_t page = page_of(it);
+                if (page < 0 || static_cast<uint32_t>(page) >= p.pool_pages) page = -1;   // raised by issue()
+                const int slot = (L - 1) & (kPageTokens - 1);
+                const uint32_t kbits = new_k, vbits = new_v;
+                uint8_t *tile_ptr = my_tiles + stage * kTileBytes;
+                const int kr = slot, vr = kPageTokens + slot;
+                auto at = [](int r, int d) { return r * 128 + ((((d >> 3) ^ (r & 7)) << 4) | ((d & 7) * 2)); };
+                *reinterpret_cast<uint16_t *>(tile_ptr + at(kr, lane)) = static_cast<uint16_t>(kbits & 0xffffu);
+                *reinterpret_cast<uint16_t *>(tile_ptr + at(kr, lane + 32)) = static_cast<uint16_t>(kbits >> 16);
+                *reinterpret_cast<uint32_t *>(tile_ptr + at(vr, 2 * lane)) = vbits;
+                if (page >= 0) {
+                    uint16_t *rows = p.pool + (static_cast<size_t>(page) * p.kv_heads + g) * (kTileRows * kHeadDim);
+                    rows[kr * kHeadDim + lane] = static_cast<uint16_t>(kbits & 0xffffu);
+                    rows[kr * kHeadDim + lane + 32] = static_cast<uint16_t>(kbits >> 16);
+                    *reinterpret_cast<uint32_t *>(rows + vr * kHeadDim + 2 * lane) = vbits;
+                }
+                __syncwarp();
+            }
+        }
         uint32_t kb[4][4], vb[4][4];
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -304,9 +403,14 @@ size_t decode_workspace_bytes(uint32_t seqs, uint32_t kv_heads, uint32_t max_spl
 
 void launch_decode(const DecodeParams &p, cudaStream_t stream) {
     // per device, so set on every launch (a process may drive more than one GPU); it is cheap
-    cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     dim3 grid(p.max_splits, p.kv_heads, p.seqs);
-    decode_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    if (p.q_new) {
+        cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        decode_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    } else {
+        cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        decode_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    }
 }
 
 }  // namespace cc

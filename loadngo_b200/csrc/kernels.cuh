@@ -51,6 +51,15 @@ struct DecodeParams {
     uint32_t window;              // 0 = all keys
     uint32_t pages_per_split, max_splits;
     float scale_log2e;            // softmax scale * log2(e)
+    // The fused decode step (q_new != null): the launch also rotates the new position's q and k
+    // and appends k and v, as launch_rope_append does for one token per sequence at position
+    // seq_lens[i] - 1; q_hi and q_lo are then not read.
+    const void *q_new, *k_new, *v_new;   // [seqs][heads][64], [seqs][kv_heads][64] x2; bf16 or f32
+    int in_f32;
+    const float *table;           // [table_rows][32][2] (cos, sin), row = position - table_start
+    int64_t table_start, table_rows;
+    uint32_t q_stride, k_stride, v_stride;  // elements between consecutive sequences' rows
+    uint16_t *pool;               // the pool the tensor map describes, for the new rows
 };
 void launch_decode(const DecodeParams &p, cudaStream_t stream);
 // Bytes of scratch `launch_decode` needs for the given sizes (partials + counters).

@@ -85,6 +85,17 @@ class PagedAttentionLayer:
             self._s(self.LENS, n * 4), n, max_seq_len, self._s(self.SINKS, h * 4) if self.has_sinks else None,
             self.window, self.scale, self._s(self.OUT, n * h * HEAD_DIM * BF16))
 
+    def record_decode_step(self, batch: compute.Batch, n: int, max_seq_len: int, in_f32: bool = False) -> None:
+        """`record_append` + `record_decode` for one new token per sequence as one launch."""
+        h, g = self.heads, self.kv_heads
+        esz = 4 if in_f32 else BF16
+        batch.attention_decode_step_paged(
+            (self._s(self.Q, n * h * HEAD_DIM * esz), self._s(self.K, n * g * HEAD_DIM * esz),
+             self._s(self.V, n * g * HEAD_DIM * esz)),
+            in_f32, self._s(self.TABLE, len(self.table)), 0, self.cache.descriptor(self.POOL, self.BT),
+            self._s(self.LENS, n * 4), n, max_seq_len, self._s(self.SINKS, h * 4) if self.has_sinks else None,
+            self.window, self.scale, self._s(self.OUT, n * h * HEAD_DIM * BF16))
+
     def record_prefill(self, batch: compute.Batch, seqs: int, total: int, max_t: int) -> None:
         h = self.heads
         batch.attention_prefill_paged(
@@ -104,9 +115,10 @@ class PagedAttentionLayer:
         self.seq_ids.write(np.asarray(seq_ids, np.int32))
         return n
 
-    def decode_step(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, seq_ids=None) -> np.ndarray:
+    def decode_step(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, seq_ids=None, fused: bool = True) -> np.ndarray:
         """One new token for each of `n` sequences: append at each sequence's next position and
-        attend.  Host arrays in, host array out (uploads and the read-back are part of it)."""
+        attend.  Host arrays in, host array out (uploads and the read-back are part of it).
+        `fused`: one launch for the step; else the append and the attention as two."""
         n = q.shape[0]
         seq_ids = np.arange(n) if seq_ids is None else np.asarray(seq_ids)
         positions = self.cache.lens[seq_ids].astype(np.int32)
@@ -118,22 +130,28 @@ class PagedAttentionLayer:
         assert np.array_equal(seq_ids, np.arange(n)), "decode_step serves sequences 0..n-1 in order"
         self.seq_lens.write((positions + 1).astype(np.int32))
         batch = self.gpu.batch(self.buffers())
-        self.record_append(batch, n)
-        self.record_decode(batch, n, int(positions.max()) + 1)
+        if fused:
+            self.record_decode_step(batch, n, int(positions.max()) + 1)
+        else:
+            self.record_append(batch, n)
+            self.record_decode(batch, n, int(positions.max()) + 1)
         batch.read_back(self._s(self.OUT, n * self.heads * HEAD_DIM * BF16))
         done = batch.run()
         if isinstance(done.gpu_time, Exception):
             raise done.gpu_time
         return self.out.view(np.uint16)[: n * self.heads * HEAD_DIM].reshape(n, self.heads, HEAD_DIM).copy()
 
-    def open_decode_loop(self, n: int, max_seq_len: int) -> None:
+    def open_decode_loop(self, n: int, max_seq_len: int, fused: bool = True) -> None:
         """Records one decode step for sequences 0..n-1 (append, attend, read the output back)
         to be replayed once per token by `decode_step_replayed`; `max_seq_len` bounds the length
         any of the sequences reaches while the loop is open (it sizes the split of long caches)."""
         self._loop_n = n
         self._loop = self.gpu.batch(self.buffers())
-        self.record_append(self._loop, n)
-        self.record_decode(self._loop, n, max_seq_len)
+        if fused:
+            self.record_decode_step(self._loop, n, max_seq_len)
+        else:
+            self.record_append(self._loop, n)
+            self.record_decode(self._loop, n, max_seq_len)
         self._loop.read_back(self._s(self.OUT, n * self.heads * HEAD_DIM * BF16))
         self._loop.end_recording()
 

@@ -290,3 +290,94 @@ def test_replayed_decode_loop_equals_fresh_batches(gpu):
     looped.close_decode_loop()
     fresh.free()
     looped.free()
+
+
+@pytest.mark.parametrize("window, ring, kv_heads", [(0, 0, 8), (128, 0, 8), (128, 12, 8), (0, 0, 1), (16, 0, 2)])
+def test_fused_decode_step_is_bit_identical_to_append_then_attend(gpu, window, ring, kv_heads):
+    """One launch per step (rotation and append inside the decode kernel) against the two launches
+    it replaces, on a ragged batch whose lengths sit on page, warp and split edges and cross them
+    while decoding: the same output bits every step, and in the end the same bits in every page."""
+    lens = [0, 1, 15, 16, 17, 63, 64, 127, 128, 129, 700, 2049, 4096 + 33]
+    steps, n = 20, len(lens)
+    sinks = np.random.default_rng(1).standard_normal(kv_heads * 8).astype(np.float32)
+    layers = []
+    for _ in range(2):
+        rng = np.random.default_rng(77)
+        layer = PagedAttentionLayer(gpu, seqs=n, max_context=4200, max_new=n, kv_heads=kv_heads, window=window,
+                                    sinks=sinks, ring_pages=ring, rng=rng, mirrored_pool=True)
+        _fill(layer, rng, lens, poison=True)
+        layers.append(layer)
+    two, one = layers
+    rng = np.random.default_rng(3)
+    for step in range(steps):
+        q = bits(rng.standard_normal((n, kv_heads * 8, D)).astype(np.float32) * 1.2)
+        k = bits(rng.standard_normal((n, kv_heads, D)).astype(np.float32))
+        v = bits(rng.standard_normal((n, kv_heads, D)).astype(np.float32))
+        a = two.decode_step(q, k, v, fused=False)
+        b = one.decode_step(q, k, v, fused=True)
+        assert not np.isnan(widen(b)).any(), f"step {step}: a poisoned row was read"
+        assert np.array_equal(a, b), f"step {step}: {np.argwhere(a != b)[:4]}"
+    assert np.array_equal(pool_view(two), pool_view(one)), "the caches differ"
+    assert np.array_equal(two.cache.lens, one.cache.lens) and list(one.cache.lens) == [l + steps for l in lens]
+    two.free(); one.free()
+
+
+def test_fused_decode_step_takes_float_inputs_and_strided_rows(gpu):
+    """q, k and v as float32 column ranges of one projection output (one row of 5120 per
+    sequence), through the raw entry, against the separate calls on the same rows."""
+    import ctypes
+    rng = np.random.default_rng(8)
+    n, lens = 3, [40, 1, 300]
+    out = []
+    for fused in (False, True):
+        r = np.random.default_rng(5)
+        layer = PagedAttentionLayer(gpu, seqs=n, max_context=512, max_new=n, sinks=np.ones(64, np.float32), rng=r,
+                                    mirrored_pool=True)
+        _fill(layer, r, lens, poison=False)
+        for s, l in enumerate(lens):
+            layer.cache.reserve(s, l + 1)
+        layer.cache.flush_table()
+        layer.pool_flush = layer.cache.pool.flush()
+        layer.cache.table.flush()
+        qkv = np.random.default_rng(9).standard_normal((n, 5120)).astype(np.float32)
+        rows = gpu.upload(qkv)
+        rows.flush()
+        layer.seq_lens.write(np.array([l + 1 for l in lens], np.int32)); layer.seq_lens.flush()
+        layer.positions.write(np.array(lens, np.int32)); layer.positions.flush()
+        layer.seq_ids.write(np.arange(n, dtype=np.int32)); layer.seq_ids.flush()
+        layer.sinks.flush(); layer.table.flush()
+        base = rows.device_ptr
+        ws_bytes = compute.lib().cc_decode_workspace_bytes(n, 8, 301, 0, 0)
+        ws = gpu.device_buffer(ws_bytes); ws.zero()
+        d = compute.DecodeArgs()
+        d.pool, d.pool_pages = layer.cache.pool.device_ptr, layer.cache.pool_pages
+        d.block_table, d.max_pages, d.ring_pages = layer.cache.table.device_ptr, layer.cache.max_pages, 0
+        d.seq_lens, d.seqs, d.max_seq_len = layer.seq_lens.device_ptr, n, 301
+        d.sinks, d.heads, d.kv_heads, d.window, d.scale = layer.sinks.device_ptr, 64, 8, 0, 0.125
+        d.out, d.workspace, d.workspace_bytes = layer.out.device_ptr, ws.device_ptr, ws_bytes
+        if fused:
+            a = compute.DecodeStepArgs()
+            a.attn = d
+            a.q, a.k, a.v, a.in_f32 = base, base + 4096 * 4, base + 4608 * 4, 1
+            a.table, a.table_start, a.table_rows = layer.table.device_ptr, 0, 512
+            a.q_row_stride = a.k_row_stride = a.v_row_stride = 5120
+            compute.check(compute.lib().cc_attention_decode_step_paged(gpu.stream, ctypes.byref(a)))
+        else:
+            r_ = compute.RopeAppendArgs()
+            r_.q, r_.k, r_.v, r_.in_f32 = base, base + 4096 * 4, base + 4608 * 4, 1
+            r_.q_hi = layer.q_rot.device_ptr; r_.q_lo = layer.q_rot.device_ptr + n * 64 * D * 2
+            r_.table, r_.table_start, r_.table_rows = layer.table.device_ptr, 0, 512
+            r_.positions, r_.seq_ids = layer.positions.device_ptr, layer.seq_ids.device_ptr
+            r_.pool, r_.pool_pages = d.pool, d.pool_pages
+            r_.block_table, r_.max_pages, r_.ring_pages = d.block_table, d.max_pages, 0
+            r_.n, r_.heads, r_.kv_heads = n, 64, 8
+            r_.q_row_stride = r_.k_row_stride = r_.v_row_stride = 5120
+            compute.check(compute.lib().cc_rope_append_paged(gpu.stream, ctypes.byref(r_)))
+            d.q_hi, d.q_lo = r_.q_hi, r_.q_lo
+            compute.check(compute.lib().cc_attention_decode_paged(gpu.stream, ctypes.byref(d)))
+        gpu.synchronize()
+        layer.out.invalidate(); layer.cache.pool.invalidate()
+        out.append((layer.out.view(np.uint16)[: n * 64 * D].copy(), pool_view(layer).copy()))
+        ws.free(); rows.free(); layer.free()
+    assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
+    assert np.abs(widen(out[1][0])).max() > 0.01
