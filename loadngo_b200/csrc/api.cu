@@ -732,6 +732,10 @@ struct cc_batch {
     std::vector<cc_slice> read_backs;
     std::vector<cc_slice> outputs;  // ranges the recorded work writes; marked device-newer at commit
     uint32_t dispatches = 0;
+    // what the dispatch recorded last writes, and its number: a dispatch that may start beside the
+    // end of the one before it checks here that it reads none of it early
+    std::vector<cc_slice> last_outputs;
+    uint32_t last_outputs_of = 0xffffffffu;
     bool replayed = false;
     // A replayed batch runs its kernels as one CUDA graph from the second replay on (captured
     // during the first): a decode step is a handful of short kernels, and launching them one by
@@ -786,7 +790,26 @@ int narrow(uint64_t n, uint32_t *out) {
     return CC_OK;
 }
 
-void wrote(cc_batch *b, const cc_slice &s) { b->outputs.push_back(s); }
+// `mirror`: false for a range whose host copy nobody reads (a pool without a mirror): it is not
+// marked device-newer at commit, but still counts as written by this dispatch.
+void wrote(cc_batch *b, const cc_slice &s, bool mirror = true) {
+    if (mirror) b->outputs.push_back(s);
+    if (b->last_outputs_of != b->dispatches) {   // entries call this before they count their dispatch
+        b->last_outputs.clear();
+        b->last_outputs_of = b->dispatches;
+    }
+    b->last_outputs.push_back(s);
+}
+
+// True when the dispatch about to be recorded follows, in this batch, a dispatch whose outputs are
+// known and touch none of `early` (what the new one reads before it waits for its predecessor).
+bool may_start_early(const cc_batch *b, std::initializer_list<const cc_slice *> early) {
+    if (b->dispatches == 0 || b->last_outputs_of + 1 != b->dispatches) return false;
+    for (const cc_slice &w : b->last_outputs)
+        for (const cc_slice *r : early)
+            if (r && overlaps(w, *r)) return false;
+    return true;
+}
 
 }  // namespace
 
@@ -1308,7 +1331,7 @@ extern "C" int cc_batch_rope_append_paged(cc_batch *b, cc_slice q, cc_slice k, c
         return launch_status("rope_append launch");
     });
     wrote(b, q_rot);
-    if (b->buffers[cache->pool.buffer]->host) wrote(b, cache->pool);  // a mirrored pool is read back lazily, whole
+    wrote(b, cache->pool, b->buffers[cache->pool.buffer]->host != nullptr);  // a mirrored pool is read back lazily, whole
     ++b->dispatches;
     return CC_OK;
 }
@@ -1422,12 +1445,15 @@ extern "C" int cc_batch_attention_decode_step_paged(cc_batch *b, cc_slice q, cc_
     if (int rc = grow_decode_scratch(b->gpu, seqs, cache->kv_heads, max_seq_len, window, &a.attn)) return rc;
     cc::DecodeParams p;
     if (int rc = decode_step_prepare(&a, &p)) return rc;
+    // Its first reads (lengths, block table, pages) may run beside the end of the dispatch before it
+    // when that one writes none of them: between the layers of a decode step nothing does.
+    p.pdl = may_start_early(b, {&seq_lens, &cache->block_table, &cache->pool}) ? 1 : 0;
     b->work.push_back([=](cudaStream_t s) {
         cc::launch_decode(p, s);
         return launch_status("decode step launch");
     });
     wrote(b, out);
-    if (b->buffers[cache->pool.buffer]->host) wrote(b, cache->pool);  // a mirrored pool is read back lazily, whole
+    wrote(b, cache->pool, b->buffers[cache->pool.buffer]->host != nullptr);  // a mirrored pool is read back lazily, whole
     ++b->dispatches;
     return CC_OK;
 }

@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_consta
     const int L = p.seq_lens[b];
     const size_t out_base = (static_cast<size_t>(b) * p.heads + static_cast<size_t>(g) * kGroup) * kHeadDim;
     if (L <= 0) {  // nothing visible: defined as zeros
+        griddep_wait();
+        griddep_launch();
         if (split == 0) {
             for (int i = tid; i < kGroup * kHeadDim; i += kThreads) p.out[out_base + i] = 0;
         }
@@ -127,6 +129,11 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_consta
                     (page * static_cast<int>(p.kv_heads) + g) * kTileRows, &my_bars[stage]);
     };
     for (int s = 0; s < kStages && s < count; ++s) issue(s);
+    // Up to here only the lengths, the block table and pages of the pool were read, and nothing was
+    // written: under a programmatic launch this part ran beside the end of the launch before.
+    // From here on its results (the inputs of this step, the scratch of the splits) are visible.
+    griddep_wait();
+    griddep_launch();
 
     // Query fragments: row r (0-7) = head r "hi", row r + 8 = the same head's "lo".
     const int hr = lane >> 2, tq = lane & 3;
@@ -406,7 +413,17 @@ void launch_decode(const DecodeParams &p, cudaStream_t stream) {
     dim3 grid(p.max_splits, p.kv_heads, p.seqs);
     if (p.q_new) {
         cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        decode_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
+        cudaLaunchConfig_t config{};
+        config.gridDim = grid;
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = kSmemBytes;
+        config.stream = stream;
+        cudaLaunchAttribute attribute{};
+        attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute.val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = &attribute;
+        config.numAttrs = p.pdl ? 1 : 0;
+        cudaLaunchKernelEx(&config, decode_kernel<true>, p);
     } else {
         cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         decode_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);

@@ -60,6 +60,10 @@ struct DecodeParams {
     int64_t table_start, table_rows;
     uint32_t q_stride, k_stride, v_stride;  // elements between consecutive sequences' rows
     uint16_t *pool;               // the pool the tensor map describes, for the new rows
+    // Launch with programmatic serialization: the kernel reads lengths, block table and its first
+    // pages while the launch before it in the stream may still run.  Only for a caller that knows
+    // that launch writes none of them.
+    int pdl;
 };
 void launch_decode(const DecodeParams &p, cudaStream_t stream);
 // Bytes of scratch `launch_decode` needs for the given sizes (partials + counters).

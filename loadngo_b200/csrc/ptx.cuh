@@ -132,4 +132,11 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     return r;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may start while the launch before it in the stream is still running; `griddep_wait` returns once
+// that launch has completed and its writes are visible, `griddep_launch` lets the launch after this
+// one start.  Without the attribute both do nothing.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace cc

@@ -381,3 +381,77 @@ def test_fused_decode_step_takes_float_inputs_and_strided_rows(gpu):
         ws.free(); rows.free(); layer.free()
     assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
     assert np.abs(widen(out[1][0])).max() > 0.01
+
+
+@pytest.mark.parametrize("order", ["alternating", "same_layer_twice"])
+def test_many_steps_in_one_batch_equal_one_step_per_batch(gpu, order):
+    """Steps of a full and a 128-window layer recorded back to back in one batch (where a step's
+    launch may begin its reads beside the end of the launch before it, when that one writes none
+    of what it reads early) against the same steps as one batch each: same outputs, same caches.
+    `same_layer_twice` puts two steps of one layer next to each other, where the second must wait."""
+    lens = [5, 16, 31, 200, 1025, 3000]
+    n, steps = len(lens), 12
+    rng0 = np.random.default_rng(2)
+    sinks = rng0.standard_normal(64).astype(np.float32)
+    q = bits(rng0.standard_normal((steps, n, 64, D)).astype(np.float32))
+    k = bits(rng0.standard_normal((steps, n, 8, D)).astype(np.float32))
+    v = bits(rng0.standard_normal((steps, n, 8, D)).astype(np.float32))
+
+    def make():
+        pair = []
+        for window in (0, 128):
+            rng = np.random.default_rng(31 + window)
+            layer = PagedAttentionLayer(gpu, seqs=n, max_context=3100, max_new=n, window=window, sinks=sinks, rng=rng,
+                                        mirrored_pool=True)
+            _fill(layer, rng, lens, poison=True)
+            for s, l in enumerate(lens):
+                layer.cache.reserve(s, l + steps)
+            layer.cache.lens[:] = lens
+            layer.cache.flush_table()
+            # every step's inputs and lengths side by side, so that one batch can hold all the steps
+            for name, data in (("q", q), ("k", k), ("v", v)):
+                getattr(layer, name).free()
+                setattr(layer, name, gpu.upload(data))
+            layer.seq_lens.free()
+            layer.seq_lens = gpu.upload((np.asarray(lens)[None, :] + np.arange(1, steps + 1)[:, None]).astype(np.int32))
+            layer.out.free()
+            layer.out = gpu.buffer(steps * n * 64 * D * 2)
+            pair.append(layer)
+        return pair
+
+    def record(batch, layer, base, step):
+        S = lambda i, off, ln: compute.Slice(base + i, off, ln)
+        cache = compute.PagedCache(S(layer.POOL, 0, len(layer.cache.pool)), S(layer.BT, 0, len(layer.cache.table)),
+                                   layer.cache.max_pages, 0, 8)
+        batch.attention_decode_step_paged(
+            (S(layer.Q, step * n * 64 * D * 2, n * 64 * D * 2), S(layer.K, step * n * 8 * D * 2, n * 8 * D * 2),
+             S(layer.V, step * n * 8 * D * 2, n * 8 * D * 2)), False, S(layer.TABLE, 0, len(layer.table)), 0, cache,
+            S(layer.LENS, step * n * 4, n * 4), n, max(lens) + steps, S(layer.SINKS, 0, 64 * 4), layer.window, layer.scale,
+            S(layer.OUT, step * n * 64 * D * 2, n * 64 * D * 2))
+
+    plan = []
+    for step in range(steps):
+        plan += [(0, step), (1, step)] if order == "alternating" else [(0, step)]
+    if order == "same_layer_twice":
+        plan += [(1, step) for step in range(steps)]
+    results = []
+    for together in (False, True):
+        pair = make()
+        buffers = pair[0].buffers() + pair[1].buffers()
+        nb = len(pair[0].buffers())
+        batch = gpu.batch(buffers) if together else None
+        for li, step in plan:
+            if not together:
+                batch = gpu.batch(buffers)
+            record(batch, pair[li], li * nb, step)
+            if not together:
+                assert not isinstance(batch.run().gpu_time, Exception)
+        if together:
+            done = batch.run()
+            assert not isinstance(done.gpu_time, Exception), done.gpu_time
+        results.append([(layer.out.view(np.uint16).copy(), pool_view(layer).copy()) for layer in pair])
+        for layer in pair:
+            layer.free()
+    for (out_a, pool_a), (out_b, pool_b) in zip(*results):
+        assert not np.isnan(widen(out_b)).any()
+        assert np.array_equal(out_a, out_b) and np.array_equal(pool_a, pool_b)
