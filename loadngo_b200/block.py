@@ -93,6 +93,23 @@ class AttentionBlock:
         check(L.cc_gemm_bf16(self.blas, s, self.x.device_ptr, self.w_qkv.device_ptr, self.qkv.device_ptr, n,
                              self.qkv_width, HIDDEN, HIDDEN, HIDDEN, self.qkv_width))
         q = self.qkv.device_ptr
+        sinks = layer.sinks.device_ptr if layer.has_sinks else None
+        if decode:
+            # one launch: the columns of the projection output are rotated, appended and attended
+            need = L.cc_decode_workspace_bytes(seqs, kvl, max_len, layer.window, 0)
+            if self.workspace is None or len(self.workspace) < need:
+                self.workspace = self.gpu.device_buffer(max(need, 1 << 20))
+                self.workspace.zero()
+            d = compute.DecodeArgs(None, None, layer.cache.pool.device_ptr, layer.cache.pool_pages,
+                                   layer.cache.table.device_ptr, layer.cache.max_pages, 0, layer.seq_lens.device_ptr, seqs,
+                                   max_len, sinks, heads, kvl, layer.window, layer.scale, layer.out.device_ptr,
+                                   self.workspace.device_ptr, len(self.workspace), 0, self.status.device_ptr)
+            step = compute.DecodeStepArgs(d, q, q + heads * HEAD_DIM * 2, q + (heads + kvl) * HEAD_DIM * 2, 0,
+                                          layer.table.device_ptr, 0, len(layer.table) // 256, self.qkv_width,
+                                          self.qkv_width, self.qkv_width)
+            check(L.cc_attention_decode_step_paged(s, ctypes.byref(step)))
+            self._project_out(n, decode=True)
+            return
         args = compute.RopeAppendArgs(
             q, q + heads * HEAD_DIM * 2, q + (heads + kvl) * HEAD_DIM * 2, 0, layer.q_rot.device_ptr,
             layer.q_rot.device_ptr + n * heads * HEAD_DIM * 2, layer.table.device_ptr, 0, len(layer.table) // 256,
@@ -100,25 +117,17 @@ class AttentionBlock:
             layer.cache.table.device_ptr, layer.cache.max_pages, 0, n, heads, kvl, self.status.device_ptr,
             self.qkv_width, self.qkv_width, self.qkv_width)
         check(L.cc_rope_append_paged(s, ctypes.byref(args)))
-        sinks = layer.sinks.device_ptr if layer.has_sinks else None
         qr = layer.q_rot.device_ptr
-        if decode:
-            need = L.cc_decode_workspace_bytes(seqs, kvl, max_len, layer.window, 0)
-            if self.workspace is None or len(self.workspace) < need:
-                self.workspace = self.gpu.device_buffer(max(need, 1 << 20))
-                self.workspace.zero()
-            d = compute.DecodeArgs(qr, qr + n * heads * HEAD_DIM * 2, layer.cache.pool.device_ptr,
-                                   layer.cache.pool_pages, layer.cache.table.device_ptr, layer.cache.max_pages, 0,
-                                   layer.seq_lens.device_ptr, seqs, max_len, sinks, heads, kvl, layer.window,
-                                   layer.scale, layer.out.device_ptr, self.workspace.device_ptr, len(self.workspace),
-                                   0, self.status.device_ptr)
-            check(L.cc_attention_decode_paged(s, ctypes.byref(d)))
-        else:
-            a = compute.PrefillArgs(qr, qr + n * heads * HEAD_DIM * 2, layer.cache.pool.device_ptr,
-                                    layer.cache.pool_pages, layer.cache.table.device_ptr, layer.cache.max_pages, 0,
-                                    layer.q_offsets.device_ptr, layer.starts.device_ptr, seqs, n, max_t, sinks, heads,
-                                    kvl, layer.window, layer.scale, layer.out.device_ptr, self.status.device_ptr)
-            check(L.cc_attention_prefill_paged(s, ctypes.byref(a)))
+        a = compute.PrefillArgs(qr, qr + n * heads * HEAD_DIM * 2, layer.cache.pool.device_ptr,
+                                layer.cache.pool_pages, layer.cache.table.device_ptr, layer.cache.max_pages, 0,
+                                layer.q_offsets.device_ptr, layer.starts.device_ptr, seqs, n, max_t, sinks, heads,
+                                kvl, layer.window, layer.scale, layer.out.device_ptr, self.status.device_ptr)
+        check(L.cc_attention_prefill_paged(s, ctypes.byref(a)))
+        self._project_out(n, decode=False)
+
+    def _project_out(self, n: int, *, decode: bool) -> None:
+        """Output projection, the sum over ranks and the residual add."""
+        L, s, layer, check = compute.lib(), self.gpu.stream, self.layer, compute.check
         if decode and self.peers is not None:
             check(L.cc_oproj_reduce_residual_bf16(self.peers, s, layer.out.device_ptr, self.w_o.device_ptr,
                                                   self.h.device_ptr, n, self.att_width, self.status.device_ptr))
