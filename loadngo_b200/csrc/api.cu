@@ -919,9 +919,11 @@ int record_q8_0(cc_batch *b, const char *what, cc_slice codes, cc_slice scales, 
     if (int rc = check(b, "x", x, ((n - 1) * x_stride + cols) * 4, 16, &px)) return rc;
     if (int rc = check(b, "y", y, ((n - 1) * y_stride + rows) * 4, 4, &py)) return rc;
     if (int rc = check_output(b, y, {&codes, &scales, &x})) return rc;
+    // one position: the matrix is fetched beside the end of the dispatch before, unless that one writes it
+    const bool early = nn == 1 && may_start_early(b, {&codes, &scales});
     b->work.push_back([=](cudaStream_t s) {
         cc::launch_q8_0(reinterpret_cast<const int8_t *>(pc), ps, reinterpret_cast<const float *>(px),
-                        reinterpret_cast<float *>(py), r, c, nn, xs, ys, s);
+                        reinterpret_cast<float *>(py), r, c, nn, xs, ys, s, early);
         return CC_OK;
     });
     wrote(b, y);

@@ -27,7 +27,7 @@ void launch_attention_grouped(const float *q, const float *k, const float *v, fl
 
 // y[p][r] = sum over c of scales[(r * cols + c) / 32] * codes[r * cols + c] * x[p][c] (q8_0.cu).
 void launch_q8_0(const int8_t *codes, const void *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
-                 uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream);
+                 uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream, bool early = false);
 
 // The routed-experts kernels (moe.cu).
 void launch_gemv_f32(const float *w, const float *x, const float *bias, float *y, uint32_t rows, uint32_t cols,

@@ -21,6 +21,7 @@
 #include <stdint.h>
 
 #include "legacy.cuh"
+#include "ptx.cuh"
 
 namespace cc {
 namespace {
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(kWarpsQ8 * 32) q8_0_gemv_kernel(const int8_t *
     const int8_t *rc = codes + static_cast<size_t>(row) * cols;
     const __half *rs = scales + static_cast<size_t>(row) * (cols / 32);
     float acc = 0.f;
+    bool waited = false;
     for (uint32_t c0 = lane * 16; c0 < cols; c0 += kChunk * kUnroll) {
         int4 q[kUnroll];
         float d[kUnroll];
@@ -126,6 +128,13 @@ __global__ void __launch_bounds__(kWarpsQ8 * 32) q8_0_gemv_kernel(const int8_t *
             const bool in = c < cols;
             q[u] = in ? *reinterpret_cast<const int4 *>(rc + c) : make_int4(0, 0, 0, 0);
             d[u] = in ? __half2float(rs[c / 32]) : 0.f;
+        }
+        if (!waited) {
+            // The matrix does not depend on the launch before this one; x does.  Under a programmatic
+            // launch the loads above are in flight while that launch ends.
+            griddep_wait();
+            griddep_launch();
+            waited = true;
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -143,22 +152,43 @@ __global__ void __launch_bounds__(kWarpsQ8 * 32) q8_0_gemv_kernel(const int8_t *
             acc = fmaf(d[u], sum, acc);
         }
     }
+    if (!waited) {   // a lane without columns
+        griddep_wait();
+        griddep_launch();
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) y[row] = acc;
 }
 
+template <int kUnroll>
+void launch_gemv(const int8_t *codes, const __half *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
+                 bool early, cudaStream_t stream) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3((rows + kWarpsQ8 - 1) / kWarpsQ8);
+    config.blockDim = dim3(kWarpsQ8 * 32);
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = early ? 1 : 0;
+    cudaLaunchKernelEx(&config, q8_0_gemv_kernel<kUnroll>, codes, scales, x, y, rows, cols);
+}
+
 }  // namespace
 
+// `early`: the launch may start (and fetch its matrix) while the launch before it in the stream still
+// runs; for a caller that knows that launch does not write the matrix.
 void launch_q8_0(const int8_t *codes, const void *scales, const float *x, float *y, uint32_t rows, uint32_t cols,
-                 uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream) {
+                 uint32_t n, uint32_t x_stride, uint32_t y_stride, cudaStream_t stream, bool early) {
     const unsigned row_blocks = (rows + kWarpsQ8 * kRowsPerWarp - 1) / (kWarpsQ8 * kRowsPerWarp);
     const __half *sc = static_cast<const __half *>(scales);
     if (n == 1) {
         if (cols <= 6 * kChunk)
-            q8_0_gemv_kernel<6><<<(rows + kWarpsQ8 - 1) / kWarpsQ8, kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols);
+            launch_gemv<6>(codes, sc, x, y, rows, cols, early, stream);
         else
-            q8_0_gemv_kernel<8><<<(rows + kWarpsQ8 - 1) / kWarpsQ8, kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols);
+            launch_gemv<8>(codes, sc, x, y, rows, cols, early, stream);
     } else if (n <= 4) {
         q8_0_kernel<4><<<dim3(row_blocks, 1), kWarpsQ8 * 32, 0, stream>>>(codes, sc, x, y, rows, cols, n, x_stride, y_stride);
     } else {
