@@ -57,6 +57,16 @@ def algorithmic_bytes(lens: np.ndarray, window: int, kv_heads: int = KV_HEADS) -
     return int(per_seq.sum())
 
 
+def bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns, round to nearest even (the synthetic inputs of the GPU arm)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
 def draw_lengths(seqs: int) -> np.ndarray:
     return np.random.default_rng(0).integers(LEN_LO, LEN_HI + 1, seqs).astype(np.int64)
 
@@ -210,7 +220,6 @@ class DecodeBench:
         self.fused = fused
         from loadngo_b200 import compute
         from loadngo_b200.layer import PagedAttentionLayer
-        from oracle import oracle  # only for bf16 rounding of the synthetic inputs
         self.compute, self.gpu = compute, gpu
         self.lens, self.kv_heads, self.heads = lens, kv_heads, kv_heads * GROUP
         self.seqs = len(lens)
@@ -231,7 +240,7 @@ class DecodeBench:
             self._fill_pool(layer, rng)
             self.layers.append(layer)
         n, h, g = self.seqs, self.heads, kv_heads
-        bf = lambda shape: oracle.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32))
+        bf = lambda shape: bf16_bits(rng.standard_normal(shape).astype(np.float32))
         self.q_host, self.k_host, self.v_host = bf((n, h, D)), bf((n, g, D)), bf((n, g, D))
         # per-step positions and lengths, all steps in one buffer
         steps = np.arange(total_steps)[:, None]
@@ -251,10 +260,9 @@ class DecodeBench:
         chunk = 64 << 20
         stage = self.gpu.buffer(min(chunk, nbytes))
         done = 0
-        from oracle import oracle
         while done < nbytes:
             size = min(chunk, nbytes - done)
-            data = oracle.f32_to_bf16_bits(rng.standard_normal(size // 2).astype(np.float32))
+            data = bf16_bits(rng.standard_normal(size // 2).astype(np.float32))
             stage.write(data)
             # a one-dispatch batch copies the staged rows into place (copy_rows works on floats)
             batch = self.gpu.batch([stage, layer.cache.pool])
@@ -412,11 +420,10 @@ class PrefillBench:
 
     def __init__(self, gpu, kv_heads):
         from loadngo_b200.layer import PagedAttentionLayer
-        from oracle import oracle  # bf16 rounding of the synthetic inputs only
         rng = np.random.default_rng(3)
         self.gpu, self.kv_heads, self.heads = gpu, kv_heads, kv_heads * GROUP
         n = self.SEQS * self.T
-        bf = lambda shape: oracle.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32))
+        bf = lambda shape: bf16_bits(rng.standard_normal(shape).astype(np.float32))
         q, k, v = bf((n, self.heads, D)), bf((n, kv_heads, D)), bf((n, kv_heads, D))
         self.layers = []
         for window in (0, WINDOW):
@@ -493,7 +500,6 @@ def run_longctx(args):
     from loadngo_b200 import compute
     from loadngo_b200.layer import PagedAttentionLayer
     from loadngo_b200.paged import shard_kv_heads
-    from oracle import oracle
     torch, dist, world, rank, local = _dist_setup()
     gpu = compute.Gpu(local)
     kvl = len(shard_kv_heads(KV_HEADS, world, rank))
@@ -515,7 +521,7 @@ def run_longctx(args):
         # one random 64 MiB block repeated through the pool: N(0,1) everywhere, set-up in seconds
         nbytes = len(layer.cache.pool)
         chunk = min(64 << 20, nbytes)
-        stage = gpu.upload(oracle.f32_to_bf16_bits(rng.standard_normal(chunk // 2).astype(np.float32)))
+        stage = gpu.upload(bf16_bits(rng.standard_normal(chunk // 2).astype(np.float32)))
         done = 0
         while done < nbytes:
             size = min(chunk, nbytes - done)
@@ -526,7 +532,7 @@ def run_longctx(args):
                 raise r.gpu_time
             done += size
         stage.free()
-        bf = lambda shape: oracle.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32))
+        bf = lambda shape: bf16_bits(rng.standard_normal(shape).astype(np.float32))
         layer.q.write(bf((seqs, heads, D))); layer.k.write(bf((seqs, kvl, D))); layer.v.write(bf((seqs, kvl, D)))
         layer.seq_ids.write(np.arange(seqs, dtype=np.int32))
         pos_all = (lens[None, :] + np.arange(steps_total)[:, None]).astype(np.int32)
@@ -597,7 +603,6 @@ def run_block(args):
     16 x 2048-token prefill then 128 decode steps."""
     from loadngo_b200 import compute
     from loadngo_b200.block import HIDDEN, AttentionBlock, make_peer_group, shard_weights
-    from oracle import oracle
     import ctypes
     torch, dist, world, rank, local = _dist_setup()
     gpu = compute.Gpu(local)
@@ -621,9 +626,9 @@ def run_block(args):
     lq, lo = shard_weights(w_qkv, w_o, world, rank)
     kvl = KV_HEADS // world
     block = AttentionBlock(gpu, seqs=seqs, max_context=T + 2 * decode_steps + 16, max_tokens=seqs * T,
-                           w_qkv=oracle.f32_to_bf16_bits(lq), w_o=oracle.f32_to_bf16_bits(lo), norm=norm,
+                           w_qkv=bf16_bits(lq), w_o=bf16_bits(lo), norm=norm,
                            sinks=sinks[rank * kvl * GROUP:(rank + 1) * kvl * GROUP], kv_local=kvl, comm=comm)
-    hidden = oracle.f32_to_bf16_bits(rng.standard_normal((seqs * T, HIDDEN)).astype(np.float32))
+    hidden = bf16_bits(rng.standard_normal((seqs * T, HIDDEN)).astype(np.float32))
     stream = torch.cuda.ExternalStream(gpu.stream)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
 
@@ -682,7 +687,7 @@ def run_block(args):
     sync()
     fused_ms = _max_over_ranks(dist, world, fused_ms) / (decode_steps - 3)
     h_fused = block._read_h(seqs)
-    finite = bool(np.isfinite(oracle.bf16_bits_to_f32(h_fused)).all())
+    finite = bool(np.isfinite(bf16_to_f32(h_fused)).all())
     if rank == 0:
         m = seqs * T
         flops = 2 * m * 5120 * HIDDEN + 2 * m * HIDDEN * 4096 + 4 * D * 64 * (T * (T + 1) // 2) * seqs
@@ -713,7 +718,6 @@ def run_q8_0(args):
     in one batch: 636 MB of codes and scales streamed once, far beyond L2.  HBM-bound; reported
     against the measured copy bandwidth, with the CPU oracle's product timed beside it."""
     from loadngo_b200 import compute
-    from oracle import oracle
     gpu = compute.Gpu(0)
     S = compute.Slice
     rng = np.random.default_rng(3)
@@ -721,7 +725,7 @@ def run_q8_0(args):
     layers = 24
     per_layer = sum(r * c for r, c in shapes)
     codes_all = rng.integers(-127, 128, layers * per_layer, dtype=np.int8).view(np.uint8)
-    scales_all = oracle.f32_to_f16_bits(rng.uniform(0.001, 0.02, layers * per_layer // 32).astype(np.float32)).view(np.uint8)
+    scales_all = rng.uniform(0.001, 0.02, layers * per_layer // 32).astype(np.float16).view(np.uint8)
     x = gpu.upload(rng.standard_normal(4096).astype(np.float32))
     y = gpu.buffer(4096 * 4 * 4)
     codes, scales = gpu.upload(codes_all), gpu.upload(scales_all)
@@ -752,6 +756,7 @@ def run_q8_0(args):
     nbytes = layers * per_layer * (1 + 2 / 32)
     peak, peak_kind = measured_peak()
     # CPU: the oracle's product for one layer's q matrix, scaled by bytes
+    from oracle import oracle
     r, c = shapes[0]
     blocks = np.zeros((r * c // 32, 34), np.uint8)
     blocks[:, 2:] = codes_all[: r * c].reshape(-1, 32)
@@ -916,7 +921,6 @@ def run_gpu(args):
         if prefill is not None:
             line["prefill"] = prefill
         if world == 1 and not args.no_cpu:
-            from oracle import oracle
             cores = 1
             per_step, timed = cpu_steps(lens, cores, args.cpu_budget)
             line["cpu_baseline"] = {
