@@ -496,7 +496,7 @@ def run_longctx(args):
     KV sharded by KV head over N GPUs, no collective.  Total work is fixed (strong scaling).  The
     18 full layers share one physical cache per GPU and the 18 window layers another: the values
     are synthetic and one layer's cache is far larger than L2, so the timing is that of 36 distinct
-    caches while set-up stays short and the N=1 point fits in memory (said in DESIGN.md)."""
+    caches while set-up stays short and the N=1 point fits in memory."""
     from loadngo_b200 import compute
     from loadngo_b200.layer import PagedAttentionLayer
     from loadngo_b200.paged import shard_kv_heads

@@ -452,8 +452,8 @@ int cc_batch_commit_wait(cc_batch *batch, double *gpu_seconds);
  * (gpt-oss/src/gpu.rs:931-992).  End with cc_batch_drop. */
 int cc_batch_end_recording(cc_batch *batch);
 int cc_batch_replay_wait(cc_batch *batch, double *gpu_seconds);
-/* Dropping a batch (apple.rs:553-561): nothing recorded runs... see INTEGRATION notes: work
- * already enqueued is waited for, buffers are handed back, no callback. */
+/* Dropping a batch (apple.rs:553-561): nothing recorded runs (a batch launches only at commit);
+ * the buffers are handed back, no callback is made. */
 void cc_batch_drop(cc_batch *batch);
 /* Dispatches recorded so far. */
 uint32_t cc_batch_dispatches(const cc_batch *batch);

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is mounted:
 
-    python tests/golden/make_tiny_golden.py /root/reference
+    python tests/golden/make_tiny_golden.py <loadngo checkout>
 
 It replays `gpt-oss/tests/fixtures/tiny` (a 4-layer random-weight gpt-oss: 4 query heads over
 2 key/value heads of 32, window 8 on even layers, YaRN with original context 64, 40 tokens;
@@ -144,7 +144,9 @@ def replay(meta, T, ids, mutation: str | None = None, record: dict | None = None
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_tiny_golden.py <loadngo checkout>")
+    root = sys.argv[1]
     meta, T, ids, want = load(root)
     want = want.reshape(len(ids), -1)
     record: dict = {}

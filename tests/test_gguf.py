@@ -11,7 +11,10 @@ from loadngo_b200 import gguf
 
 from tests import gguf_writer as w
 
-TINY = "/root/reference/gpt-oss/tests/fixtures/tiny/model.gguf"
+# a loadngo checkout named by LOADNGO_REFERENCE, or lying beside this repository
+REFERENCE = os.environ.get("LOADNGO_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
+    os.path.abspath(__file__)))), "reference")
+TINY = os.path.join(REFERENCE, "gpt-oss", "tests", "fixtures", "tiny", "model.gguf")
 
 
 def sample() -> bytes:
