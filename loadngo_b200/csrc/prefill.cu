@@ -185,56 +185,81 @@ constexpr int kColsPerThread = 64;
 // First sweep: the maximum of this thread's scores.  `col0` is the tile column of the first one;
 // `lo_col..hi_col` are the visible columns of the row in this key tile (used on edge tiles only).
 template <bool kEdge>
+__device__ __forceinline__ void max16(const uint32_t (&s)[16], int col, int lo_col, int hi_col, float &mx0, float &mx1,
+                                      float &mx2, float &mx3) {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        v[i] = (kEdge && (col + i > hi_col || col + i < lo_col)) ? neg_inf_f() : __uint_as_float(s[i]);
+    mx0 = fmax3(mx0, v[0], v[1]);
+    mx1 = fmax3(mx1, v[2], v[3]);
+    mx2 = fmax3(mx2, v[4], v[5]);
+    mx3 = fmax3(mx3, v[6], v[7]);
+    mx0 = fmax3(mx0, v[8], v[9]);
+    mx1 = fmax3(mx1, v[10], v[11]);
+    mx2 = fmax3(mx2, v[12], v[13]);
+    mx3 = fmax3(mx3, v[14], v[15]);
+}
+
+// First sweep: the row maximum of this thread's 64 score columns.  The scores come from tensor memory
+// in pieces of 16 columns, the next piece on its way while the current one is used; the loop stays
+// rolled (two trips of 32 columns): unrolled, the kernel is bound by instruction fetch.
+template <bool kEdge>
 __device__ __forceinline__ float row_max_sweep(uint32_t s_addr, int col0, int lo_col, int hi_col) {
     float mx0 = neg_inf_f(), mx1 = neg_inf_f(), mx2 = neg_inf_f(), mx3 = neg_inf_f();
+    uint32_t a[16], b[16];
+    tmem_ld_x16(s_addr, a);
+    tmem_wait_ld();
 #pragma unroll 1
     for (int c = 0; c < kColsPerThread / 32; ++c) {
-        uint32_t s[32];
-        tmem_ld_x32(s_addr + c * 32, s);
+        tmem_ld_x16(s_addr + c * 32 + 16, b);
+        max16<kEdge>(a, col0 + c * 32, lo_col, hi_col, mx0, mx1, mx2, mx3);
         tmem_wait_ld();
-        if (kEdge) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int col = col0 + c * 32 + i;
-                if (col > hi_col || col < lo_col) s[i] = 0xff800000u;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-            mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-            mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-            mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-            mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-        }
+        if (c + 1 < kColsPerThread / 32) tmem_ld_x16(s_addr + c * 32 + 32, a);
+        max16<kEdge>(b, col0 + c * 32 + 16, lo_col, hi_col, mx0, mx1, mx2, mx3);
+        if (c + 1 < kColsPerThread / 32) tmem_wait_ld();
     }
     return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 }
 
+template <bool kEdge>
+__device__ __forceinline__ void exp16(const uint32_t (&s)[16], uint32_t p_addr, int col, int lo_col, int hi_col,
+                                      float2 scale2, float2 neg_m2, float2 &l_acc) {
+    uint32_t w[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        uint32_t s0 = s[2 * e], s1 = s[2 * e + 1];
+        if (kEdge) {
+            if (col + 2 * e > hi_col || col + 2 * e < lo_col) s0 = 0xff800000u;
+            if (col + 2 * e + 1 > hi_col || col + 2 * e + 1 < lo_col) s1 = 0xff800000u;
+        }
+        const float2 x = ffma2(make_float2(__uint_as_float(s0), __uint_as_float(s1)), scale2, neg_m2);
+        const uint32_t pair = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
+        w[e] = pair;
+        l_acc = fadd2(l_acc, make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u)));
+    }
+    tmem_st_x8(p_addr, w);
+}
+
 // Second sweep: P = exp2(s * scale - m) as packed bf16 pairs, written to `p_addr` (32 columns,
 // behind the scores already read); returns the sum of the rounded weights, the ones the product uses.
+// Pieces of 16 columns, the next one on its way while the current one is used, as in the first sweep.
 template <bool kEdge>
 __device__ __forceinline__ float exp_sweep(uint32_t s_addr, uint32_t p_addr, int col0, int lo_col, int hi_col, float scale,
                                            float m_use) {
     const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_use, -m_use);
     float2 l_acc = make_float2(0.f, 0.f);
+    uint32_t a[16], b[16];
+    tmem_ld_x16(s_addr, a);
+    tmem_wait_ld();
 #pragma unroll 1
     for (int c = 0; c < kColsPerThread / 32; ++c) {
-        uint32_t s[32], w[16];
-        tmem_ld_x32(s_addr + c * 32, s);
+        tmem_ld_x16(s_addr + c * 32 + 16, b);
+        exp16<kEdge>(a, p_addr + c * 16, col0 + c * 32, lo_col, hi_col, scale2, neg_m2, l_acc);
         tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            if (kEdge) {
-                const int col = col0 + c * 32 + 2 * e;
-                if (col > hi_col || col < lo_col) s[2 * e] = 0xff800000u;
-                if (col + 1 > hi_col || col + 1 < lo_col) s[2 * e + 1] = 0xff800000u;
-            }
-            const float2 x = ffma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), scale2, neg_m2);
-            const uint32_t pair = pack_bf16x2_fast(ex2(x.x), ex2(x.y));
-            w[e] = pair;
-            l_acc = fadd2(l_acc, make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u)));
-        }
-        tmem_st_x16(p_addr + c * 16, w);
+        if (c + 1 < kColsPerThread / 32) tmem_ld_x16(s_addr + c * 32 + 32, a);
+        exp16<kEdge>(b, p_addr + c * 16 + 8, col0 + c * 32 + 16, lo_col, hi_col, scale2, neg_m2, l_acc);
+        if (c + 1 < kColsPerThread / 32) tmem_wait_ld();
     }
     return l_acc.x + l_acc.y;
 }
