@@ -72,30 +72,39 @@ def draw_lengths(seqs: int) -> np.ndarray:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs.  The sampler is
+    started ahead of the region (nvidia-smi takes a moment to print its first line) and every line is
+    stamped on arrival; the summary uses the lines that arrived inside the region, or, for a region
+    shorter than the sampling period, the lines nearest to it on either side."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device: int):
-        self.device, self.rows, self.proc = device, [], None
+        self.device, self.rows, self.proc, self.t0, self.t1 = device, [], None, None, None
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            waited = time.monotonic()
+            while not self.rows and time.monotonic() - waited < 5.0:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def begin(self):
+        self.t0 = time.monotonic()
 
-    def __exit__(self, *exc):
+    def end(self):
+        self.t1 = time.monotonic()
+
+    def stop(self):
         if self.proc:
+            time.sleep(0.03)   # one more line after the region
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
@@ -103,21 +112,41 @@ class ClockSampler:
                 self.proc.kill()
             self.thread.join(timeout=2)
 
+    def __enter__(self):
+        self.start()
+        self.begin()
+        return self
+
+    def __exit__(self, *exc):
+        self.end()
+        self.stop()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
+
     def summary(self):
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        parsed = []
+        for stamp, r in self.rows:
             try:
-                sm.append(float(r[0])); mx.append(float(r[1]))
+                parsed.append((stamp, float(r[0]), float(r[1]), [n for n, flag in zip(names, r[2:6])
+                                                                  if flag.lower().startswith("active")]))
             except (ValueError, IndexError):
                 continue
-            for name, flag in zip(names, r[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+        if not parsed:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        t0, t1 = self.t0 or parsed[0][0], self.t1 or parsed[-1][0]
+        inside = [x for x in parsed if t0 <= x[0] <= t1]
+        where = "inside the timed region"
+        if not inside:   # a region shorter than the sampling period: the lines around it
+            before = [x for x in parsed if x[0] < t0][-1:]
+            after = [x for x in parsed if x[0] > t1][:1]
+            inside = before + after
+            where = "the lines nearest the timed region (it is shorter than the sampling period)"
+        reasons = sorted({n for x in inside for n in x[3]})
+        return {"sm_mhz": float(np.median([x[1] for x in inside])), "sm_max_mhz": float(max(x[2] for x in inside)),
+                "reasons": reasons, "samples": len(inside), "sampled": where}
 
 
 def measured_peak():
@@ -837,11 +866,14 @@ def run_gpu(args):
     bench = DecodeBench(gpu, lens, len(heads_here), total_steps * 3 + 2, fused=not args.unfused)
 
     # ---- resident run: `value` ----------------------------------------------------------
+    clocks = ClockSampler(local).start()
     bench.resident_run(0, args.warmup)
     barrier()
-    with ClockSampler(local) as clocks:
-        gpu_s, launches, chunk = bench.graph_run(args.warmup, args.steps)
-        barrier()
+    clocks.begin()
+    gpu_s, launches, chunk = bench.graph_run(args.warmup, args.steps)
+    barrier()
+    clocks.end()
+    clocks.stop()
     gpu_s = max_over_ranks(gpu_s)
     step_bytes_rank = float(np.mean([bench.step_bytes(args.warmup + i) for i in range(chunk)]))
     total_bytes = step_bytes_rank * world  # every rank reads its heads of every sequence: same bytes
