@@ -288,6 +288,8 @@ const void *cc_buffer_as_bytes(cc_buffer *buffer);
 void *cc_buffer_as_bytes_mut(cc_buffer *buffer);
 /* Like as_bytes_mut for one byte range: only that range is uploaded. */
 void *cc_buffer_write_range(cc_buffer *buffer, size_t offset, size_t len);
+/* cc_buffer_write_range followed by a copy of `len` bytes from `src` into the range. */
+int cc_buffer_write(cc_buffer *buffer, size_t offset, const void *src, size_t len);
 /* The device address (for raw entries). */
 void *cc_buffer_device_ptr(cc_buffer *buffer);
 /* For callers that mix buffers with the raw entries: flush enqueues, on the gpu's stream, the

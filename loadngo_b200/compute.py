@@ -176,6 +176,7 @@ SYMBOLS = {
     "cc_buffer_as_bytes": (c_void_p, [c_void_p]),
     "cc_buffer_as_bytes_mut": (c_void_p, [c_void_p]),
     "cc_buffer_write_range": (c_void_p, [c_void_p, c_size_t, c_size_t]),
+    "cc_buffer_write": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t]),
     "cc_buffer_device_ptr": (c_void_p, [c_void_p]),
     "cc_buffer_zero": (c_int, [c_void_p]),
     "cc_buffer_flush": (c_int, [c_void_p]),
@@ -328,11 +329,8 @@ class Buffer:
 
     def write(self, array: np.ndarray, offset: int = 0) -> None:
         """Copies `array`'s bytes to `offset` and marks just that range for upload."""
-        data = np.ascontiguousarray(array).view(np.uint8).reshape(-1)
-        ptr = lib().cc_buffer_write_range(self._h, offset, data.size)
-        if not ptr:
-            raise DispatchError(lib().cc_last_error().decode())
-        ctypes.memmove(ptr, data.ctypes.data, data.size)
+        data = np.ascontiguousarray(array)
+        check(lib().cc_buffer_write(self._h, offset, data.ctypes.data, data.nbytes))
 
     def zero(self) -> None:
         check(lib().cc_buffer_zero(self._h))

@@ -662,6 +662,14 @@ extern "C" void *cc_buffer_write_range(cc_buffer *b, size_t offset, size_t len) 
 }
 extern "C" void *cc_buffer_as_bytes_mut(cc_buffer *b) { return b ? cc_buffer_write_range(b, 0, b->len) : nullptr; }
 
+extern "C" int cc_buffer_write(cc_buffer *b, size_t offset, const void *src, size_t len) {
+    if (!src && len) return fail(CC_DISPATCH, "buffer: null source");
+    void *dst = cc_buffer_write_range(b, offset, len);
+    if (!dst) return CC_DISPATCH;
+    memcpy(dst, src, len);
+    return CC_OK;
+}
+
 extern "C" int cc_buffer_flush(cc_buffer *b) {
     if (!b) return fail(CC_DISPATCH, "buffer: null");
     if (b->in_flight.load(std::memory_order_acquire)) return fail(CC_DISPATCH, "buffer: a batch owns it");
