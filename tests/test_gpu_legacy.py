@@ -409,3 +409,55 @@ def test_tiny_fixture_whole_encode_attention_with_the_stored_q8_0_weights(gpu, c
         for v in res.values():
             for r in (v if isinstance(v, tuple) else (v,)):
                 r.free()
+
+
+def test_host_ranges_of_any_size_and_offset_reach_the_device_and_come_back(gpu):
+    """A buffer's two copies stay in step however the host writes it: whole, a few bytes at an odd
+    offset (the range is rounded out to 16 bytes for the copy kernel; the bytes around it must
+    survive), next to a range the device wrote in the meantime, and as a range large enough to go
+    through the copy engine instead.  Read back lazily and with an explicit read-back."""
+    rng = np.random.default_rng(4)
+    n = 1000                                           # not a multiple of 16: the tail is padding
+    a, b = gpu.buffer(n), gpu.buffer(n)
+    want = rng.integers(0, 256, n, dtype=np.uint8)
+    a.write(want)
+
+    def copy(src, dst, read_back=False):               # dst <- src on the device (250 floats)
+        batch = gpu.batch([src, dst])
+        batch.copy_rows((Slice(0, 0, n), 250), (Slice(1, 0, n), 250), 1, 250)
+        if read_back:
+            batch.read_back(Slice(1, 0, n))
+        assert not isinstance(batch.run().gpu_time, Exception)
+
+    copy(a, b)
+    assert np.array_equal(b.as_bytes()[:n], want)
+    # six bytes at an odd offset
+    patch = np.array([1, 2, 3, 4, 5, 6], np.uint8)
+    a.write(patch, offset=35)
+    want[35:41] = patch
+    copy(a, b, read_back=True)
+    assert np.array_equal(b.as_bytes()[:n], want)
+    # the device writes a range of `a` (rows 4..7 of b's floats), then the host writes beside it
+    batch = gpu.batch([b, a])
+    batch.copy_rows((Slice(0, 400, 64), 16), (Slice(1, 64, 64), 16), 1, 16)
+    assert not isinstance(batch.run().gpu_time, Exception)
+    want[64:128] = want[400:464]
+    a.write(np.array([9, 8, 7], np.uint8), offset=129)
+    want[129:132] = [9, 8, 7]
+    a.write(np.array([42], np.uint8), offset=n - 1)    # the last byte before the padding
+    want[n - 1] = 42
+    copy(a, b)
+    assert np.array_equal(b.as_bytes()[:n], want)
+    assert np.array_equal(a.as_bytes()[:n], want)
+    # a range above the copy kernel's limit takes the copy engine
+    big_n = (3 << 20) + 8
+    big, back = gpu.buffer(big_n), gpu.buffer(big_n)
+    data = rng.integers(0, 256, big_n, dtype=np.uint8)
+    big.write(data)
+    batch = gpu.batch([big, back])
+    batch.copy_rows((Slice(0, 0, big_n), big_n // 4), (Slice(1, 0, big_n), big_n // 4), 1, big_n // 4)
+    batch.read_back(Slice(1, 0, big_n))
+    assert not isinstance(batch.run().gpu_time, Exception)
+    assert np.array_equal(back.as_bytes()[:big_n], data)
+    for buf in (a, b, big, back):
+        buf.free()
