@@ -167,7 +167,7 @@ struct Cursor {
                 if (depth > 0) return invalid("nested metadata arrays");
                 uint64_t n;
                 if (!scalar(&out->element_type) || !length(&n)) return false;
-                out->items.reserve(n);
+                out->items.reserve(n < 65536 ? n : 65536);   // a count is only known to be below the bytes at hand
                 for (uint64_t i = 0; i < n; ++i) {
                     out->items.emplace_back();
                     if (!value(out->element_type, depth + 1, &out->items.back())) return false;
@@ -226,7 +226,7 @@ int parse(const uint8_t *prefix, uint64_t prefix_len, uint64_t file_len, cc_gguf
     }
     struct Described { std::string name; std::vector<uint64_t> dims; uint32_t type; uint64_t relative; };
     std::vector<Described> described;
-    described.reserve(tensor_count);
+    described.reserve(tensor_count < 65536 ? tensor_count : 65536);
     for (uint64_t i = 0; i < tensor_count; ++i) {
         Described d;
         uint32_t n_dims;
