@@ -435,6 +435,7 @@ struct Pending {
     cc_completion_fn done = nullptr;
     void *user = nullptr;
     std::string submit_error;  // a launch that failed at commit time
+    uint32_t status_slot = 0;  // which word of the gpu's host status ring this job's device status lands in
     bool stop = false;
 };
 
@@ -442,7 +443,8 @@ struct cc_gpu {
     int device = 0;
     cudaStream_t stream = nullptr;
     uint32_t *status_dev = nullptr;
-    uint32_t *status_host = nullptr;  // pinned
+    uint32_t *status_host = nullptr;  // pinned: a ring of kStatusSlots words, one per job in flight
+    std::atomic<uint32_t> next_status_slot{0};
     uint32_t *status_host_alias = nullptr;  // as kernels see it, or null
     uint8_t *scratch = nullptr;       // decode workspace, grown on demand
     size_t scratch_bytes = 0;
@@ -483,7 +485,7 @@ int finish(cc_gpu *gpu, Pending &job, std::string *message_out, double *seconds_
         float ms = 0.f;
         if (cudaEventElapsedTime(&ms, job.begin, job.end) == cudaSuccess) seconds = ms * 1e-3;
         if (!message.empty()) status = CC_GPU;
-        const uint32_t dev_status = *gpu->status_host;
+        const uint32_t dev_status = gpu->status_host[job.status_slot];
         if (dev_status != 0 && status == CC_OK) {
             status = CC_GPU;
             message = status_text(dev_status);
@@ -541,7 +543,7 @@ extern "C" int cc_gpu_new(int device, cc_gpu **out) {
     CUDA_TRY(cudaMalloc(&gpu->status_dev, 256));
     CUDA_TRY(cudaMemset(gpu->status_dev, 0, 256));
     CUDA_TRY(cudaHostAlloc(&gpu->status_host, 256, cudaHostAllocMapped | cudaHostAllocPortable));
-    *gpu->status_host = 0;
+    memset(gpu->status_host, 0, 256);
     {
         void *alias = nullptr;
         if (cudaHostGetDevicePointer(&alias, gpu->status_host, 0) == cudaSuccess) gpu->status_host_alias = static_cast<uint32_t *>(alias);
@@ -1529,6 +1531,7 @@ namespace {
 // ranges of one direction go through one kernel that reads or writes the pinned, mapped host
 // memory directly over PCIe, sixteen bytes per thread and four loads in flight per thread.
 // Ranges larger than kKernelCopyLimit keep going to the copy engine.
+constexpr uint32_t kStatusSlots = 64;   // of 4 bytes: the 256-byte host status area
 constexpr int kMaxRanges = 24;
 constexpr size_t kKernelCopyLimit = 2u << 20;
 struct CopyRange {
@@ -1675,13 +1678,16 @@ int submit(cc_batch *b, cc_completion_fn done, void *user, bool keep = false, Pe
         if (rb.offset <= buf->dev_dirty_lo && rb.offset + rb.len >= buf->dev_dirty_hi)
             buf->dev_dirty_lo = buf->dev_dirty_hi = 0;
     }
+    // Each job has its own word on the host side: batches committed one after another must not
+    // overwrite each other's status before their completions are read.
+    job.status_slot = gpu->next_status_slot.fetch_add(1, std::memory_order_relaxed) % kStatusSlots;
     if (gpu->status_host_alias) {   // the status word travels with the last read-back launch
-        list.p.status_dst = gpu->status_host_alias;
+        list.p.status_dst = gpu->status_host_alias + job.status_slot;
         list.p.status_src = gpu->status_dev;
         list.launch(s);
     } else {
         list.launch(s);
-        cudaMemcpyAsync(gpu->status_host, gpu->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+        cudaMemcpyAsync(gpu->status_host + job.status_slot, gpu->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
         cudaMemsetAsync(gpu->status_dev, 0, sizeof(uint32_t), s);
     }
     cudaEventRecord(job.end, s);
