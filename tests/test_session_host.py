@@ -283,3 +283,66 @@ def test_a_failed_batch_is_reported_after_every_buffer_came_back(model):
         FakeBatch._finish = real
     assert len(s) == 0, "a failed pair does not advance the session"
     assert all(b.owner is None for b in s.sets[0] + s.sets[1] + s.caches)
+
+
+def test_host_repacking_is_the_oracles(model):
+    """The two repackings done while loading (Q8_0 blocks split into codes and scales,
+    weights/src/q8_0.rs:17-31; MXFP4 blocks from ggml's nibble order to pairs,
+    weights/src/mxfp4.rs:119-149) against the oracle's restatements, on the fixture's tensors."""
+    from loadngo_b200.gpt_oss import ggml_to_ocp, split_q8_0
+    from oracle import oracle
+    _, _, _, g = model
+    blocks = np.ascontiguousarray(g["l1_attn_q_q8_0"])
+    n = blocks.size // 34
+    codes, scales = np.zeros(n * 32, np.uint8), np.zeros(n * 2, np.uint8)
+    oracle.lib().oracle_q8_0_split(blocks, n, codes, scales)
+    mine = split_q8_0(blocks)
+    assert np.array_equal(mine[0], codes) and np.array_equal(mine[1], scales)
+    mx = np.ascontiguousarray(g["l2_ffn_down_exps_mxfp4"])
+    want = oracle.mxfp4_ggml_to_ocp(mx)
+    got = ggml_to_ocp(mx)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+
+
+def test_cpu_routing_of_a_prompt_pass_is_the_oracles_and_gathers_rows_by_expert(model):
+    """`route_and_gather` (gpt-oss/src/gpu.rs:1187-1227) on the fixture's inputs of layer 1's experts:
+    the experts and weights of every position are the oracle's router's (ties to the lower index,
+    softmax over the chosen ones), and the gathered buffer holds each expert's rows together, an
+    expert with 32 rows or more padded to a multiple of 32."""
+    from loadngo_b200.gpt_oss import X, XE
+    from oracle import oracle
+    made, _, _, g = model
+    m = made(40)
+    s = m.session()
+    c, layer, n = m.config, 1, 40
+    x = np.ascontiguousarray(g["l1_x_ffn"][:n], np.float32)
+    s.sets[0][X].write(x)
+    by_expert, runs = m.route_and_gather(s.sets[0], layer, n)
+    w, bias = g["l1_router"].reshape(c.experts, c.hidden), g["l1_router_bias"]
+    chosen = {}
+    for e, rows in enumerate(by_expert):
+        for p, weight in rows:
+            chosen.setdefault(p, []).append((e, weight))
+    for p in range(n):
+        logits = np.ascontiguousarray((x[p] @ w.T + bias).astype(np.float32))
+        ids, weights = np.zeros(c.experts_used, np.int32), np.zeros(c.experts_used, np.float32)
+        oracle.lib().oracle_route(logits, c.experts, c.experts_used, ids, weights)
+        got = dict(chosen[p])
+        assert sorted(got) == sorted(int(i) for i in ids)
+        for i, wt in zip(ids, weights):
+            assert abs(got[int(i)] - wt) <= 1e-6
+        assert abs(sum(got.values()) - 1.0) <= 1e-6
+    # rows of an expert lie together, in position order, runs of 32 or more padded to 32
+    gathered = s.sets[0][XE].as_f32()
+    at = 0
+    for e, first, count in runs:
+        assert first == at and count == len(by_expert[e])
+        for i, (p, _) in enumerate(by_expert[e]):
+            assert np.array_equal(gathered[(first + i) * c.hidden:(first + i + 1) * c.hidden], x[p])
+        at += -(-count // 32) * 32 if count >= 32 else count
+    assert sum(count for _, _, count in runs) == n * c.experts_used
+    # a tie goes to the expert with the lower index
+    logits = np.array([1.0, 3.0, 3.0, 0.5], np.float32)
+    ids, weights = np.zeros(2, np.int32), np.zeros(2, np.float32)
+    oracle.lib().oracle_route(logits, 4, 2, ids, weights)
+    assert list(ids) == [1, 2] and weights[0] == weights[1] == 0.5
