@@ -141,3 +141,25 @@ def test_two_ranks_over_gloo_agree_on_time_and_share_an_id():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          env=dict(env, RANK="1", LOCAL_RANK="1"), capture_output=True, text=True, timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_reference_arm_under_torchrun_prints_one_line_from_rank_0():
+    """`bench.py --impl reference` launched as the scaling run launches it (two ranks): rank 0 alone
+    times the CPU restatement and prints the line, the other rank exits 0 without work."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+         "--master-port", "29541", os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+         "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = [l for l in run.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["unit"] == "GB/s" and line["higher_is_better"]
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["cpu_baseline"]["value"] == line["value"] == line["e2e"]["value"] > 0
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert line["config"]["global_batch"] == 64
