@@ -201,3 +201,32 @@ def test_the_tiny_model_written_from_the_golden_vectors_gives_the_reference_shap
     raw = path.read_bytes().replace(b"\x07\x00\x00\x00\x00\x00\x00\x00gpt-oss", b"\x07\x00\x00\x00\x00\x00\x00\x00gpt-0ss", 1)
     with pytest.raises(ConfigError, match="architecture"):
         Config.from_gguf(gguf.Gguf.parse(raw, len(raw)))
+
+
+def test_damaged_headers_are_refused_or_read_never_worse():
+    """The reader is native code that reads files nobody vouches for: every truncation of a valid
+    file and a few thousand seeded byte changes either parse (and then every sized tensor lies inside
+    the file) or are refused with one of the reader's errors."""
+    raw = sample()
+    rng = np.random.default_rng(12)
+    cases = [raw[:n] for n in range(0, len(raw), 3)]
+    for _ in range(3000):
+        damaged = bytearray(raw)
+        for _ in range(int(rng.integers(1, 4))):
+            at = int(rng.integers(0, 400))              # the header: counts, lengths, types, offsets
+            damaged[at] = int(rng.integers(0, 256))
+        cases.append(bytes(damaged))
+    parsed = refused = 0
+    for data in cases:
+        try:
+            g = gguf.Gguf.parse(data, len(data))
+        except gguf.GgufError:
+            refused += 1
+            continue
+        parsed += 1
+        for t in g.tensors:
+            assert t.len is None or t.offset + t.len <= len(data)
+        for key in g.keys():
+            g.get(key)
+        g.close()
+    assert parsed > 0 and refused > 0
